@@ -47,7 +47,7 @@ struct PrefillParams {
 };
 
 // POLY: how many of every 4 exponentials go to a polynomial instead of MUFU.EX2 (NVLLM_PREFILL_POLY): 1 / 2 / 3 with the
-// floor-based polynomial (the first version; its FRND / F2I also run on the XU pipe, so 2 and 3 gain nothing over 1),
+// floor-based polynomial (the first version; its floor and float-to-int also run on the XU pipe, so 2 and 3 gain nothing over 1),
 // 4 / 5 / 6 = 1/4, 1/2, 3/4 with the XU-free polynomial.  Default 4 (measured best: profiles/r01_prefill_microbench_v5_polysplit.jsonl).
 template <int POLY>
 __global__ void __launch_bounds__(pf::kThreads, 1)
@@ -211,8 +211,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       return __int_as_float(__float_as_int(pfr) + (static_cast<int>(n) << 23));
     };
 
-    // The same without any XU-pipe instruction (the ncu source page of round 1 shows FRND.FLOOR and F2I.FLOOR of the
-    // version above on the XU pipe next to MUFU.EX2 — it relieves nothing): round-to-nearest by the 1.5 * 2^23 magic add,
+    // The same without any XU-pipe instruction (the floor and float-to-int of the version above run on the
+    // XU pipe next to the exponentials, whose counter is saturated — it relieves nothing): round-to-nearest by the 1.5 * 2^23 magic add,
     // f in [-0.5, 0.5], degree-3 minimax polynomial (rel. err 7.5e-5), n taken from the low mantissa bits of the sum.
     auto exp2_poly2 = [](float x) {
       x = fmaxf(x, -126.f);
