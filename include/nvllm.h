@@ -338,6 +338,79 @@ int nvllm_init_weight(void* w, int64_t count, uint64_t seed, uint64_t tensor_id,
                       int32_t dtype, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Mechanisms of architectures beyond the reference's Qwen3 (no counterpart in the reference).  Operands are bf16 or
+ * f32 (`dtype`); norm parameters, router tables and the residual stream are f32.  All are legal inside graph capture.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* y[b][m, n] = sum_k x[b][m, k] * w[b][n, k] for b < batch, with element strides bsx / bsw / bsy between batch items
+ * (per-head projections).  Any sizes and strides; f32 accumulation in ascending k.  Dense bf16 problems that meet the rules
+ * of nvllm_gemm_bf16 are forwarded to it (tensor cores); the rest runs on a CUDA-core tile kernel.  f32 operands need an
+ * f32 output. */
+int nvllm_linear(void* y, const void* x, const void* w, int32_t m, int32_t n, int32_t k, int64_t ldx, int64_t ldw,
+                 int64_t ldy, int32_t batch, int64_t bsx, int64_t bsw, int64_t bsy, int32_t dtype, int32_t out_dtype,
+                 void* stream);
+/* Grouped variant for expert layers.  Rows are cut into 32-row tiles; tile i uses the weights of group tile_group[i]
+ * (w + group * group_stride_w; < 0: tile unused).  row_src (nullable): row r reads x[row_src[r]] (< 0: padding row, not
+ * written).  glu != 0: every group's weights are [gate rows (n) | up rows (n)] x k and the output is
+ * min(g, limit) * sigmoid(1.702 * min(g, limit)) * (clamp(u, -limit, limit) + 1), g and u rounded to the operand type first. */
+int nvllm_linear_grouped(void* y, const void* x, const void* w, int32_t max_rows, int32_t n, int32_t k, int64_t ldx,
+                         int64_t ldw, int64_t ldy, int64_t group_stride_w, const int32_t* row_src,
+                         const int32_t* tile_group, int32_t glu, float limit, int32_t dtype, int32_t out_dtype,
+                         void* stream);
+/* out[i, c] = the same clamped gated activation of gate_up[i, c] and gate_up[i, ff + c]; gate_up is [n, 2 ff]. */
+int nvllm_glu_clamped(void* out, const void* gate_up, int32_t n, int32_t ff, float limit, int32_t dtype, void* stream);
+
+/* Dynamic Tanh normalisation, dyt(x) = tanh(alpha x) w + b (no mean, no variance), fused around an f32 residual stream:
+ *   y != NULL:   h += dyt_post(y)        out != NULL:   out = dyt_pre(h)      (h: f32 [n, hidden], updated in place) */
+int nvllm_dyt_residual_norm(void* out, float* h, const void* y, const float* post_alpha, const float* post_w,
+                            const float* post_b, const float* pre_alpha, const float* pre_w, const float* pre_b, int32_t n,
+                            int32_t hidden, int32_t dtype, void* stream);
+/* h[i, :] = table[ids[i], :] as f32 (ids clamped to the table). */
+int nvllm_embedding_gather_f32(float* h, const void* table, const int64_t* ids, int32_t n, int32_t hidden, int32_t vocab,
+                               int32_t table_dtype, void* stream);
+/* out[i, :] = x[rows[i], :]  (rows clamped to [0, n_src)). */
+int nvllm_gather_rows(void* out, const void* x, const int32_t* rows, int32_t n, int32_t hidden, int32_t n_src, int32_t dtype,
+                      void* stream);
+
+/* Rotary table for the interleaved pairing (dimension 2i with 2i+1): cos_sin[p][i] = (cos, sin)(p * base^(-2i/dims)),
+ * i < dims/2, p < max_pos, angles computed in f64.  f32 [max_pos, dims/2, 2]. */
+int nvllm_rope_table_interleaved(float* cos_sin, int32_t max_pos, int32_t dims, double base, void* stream);
+/* Latent attention, per-token preparation.  dkv row = [kv_rank latent | rot_dim shared key part]; q row = heads x
+ * [dim | rot_dim].  The latent is RMS-normed (x / sqrt(mean(x^2) + eps) * c_norm_w) and the key part rotated (first rot_dims
+ * values, interleaved pairs) into cache row slots[i] ([kv_rank | rot_dim], cache_row elements apart; slot < 0: nothing
+ * stored); the rotated part of every query head is rotated in place. */
+int nvllm_latent_prepare(void* q, int64_t ldq, const void* dkv, int64_t lddkv, const float* c_norm_w, float eps,
+                         const int64_t* positions, const float* rope_table, int32_t rot_dims, int32_t max_pos, int32_t n,
+                         int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, void* cache, int64_t cache_row,
+                         const int32_t* slots, int32_t dtype, void* stream);
+/* Latent attention over the paged cache with the key up-projection folded into the queries:
+ *   s[t, h, j] = scale * (q_abs[t, h, :] . c_j + q[t, h, dim:] . k_rot_j),  j <= positions[t] in sequence tok_seq[t]
+ *   out[t, h, :] = sum_j softmax_j(s) c_j                                   (kv_rank values per head)
+ * q_abs: f32 [n, heads, kv_rank]; block_tables: [sequences, table_cap] (entries < 0 end a sequence's keys). */
+int nvllm_latent_attention(void* out, int64_t ldo, const float* q_abs, int64_t ldqa, const void* q, int64_t ldq,
+                           const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
+                           int32_t table_cap, int32_t block_size, const void* cache, int64_t cache_row, int32_t n,
+                           int32_t heads, int32_t dim, int32_t rot_dim, int32_t kv_rank, float scale, int32_t dtype,
+                           void* stream);
+
+/* Mixture-of-experts routing.  logits: f32 [n, outputs] (real experts first, identity experts last).
+ *   s = softmax(logits); chosen = the `top` largest of s + bias (bias nullable; ties: lowest index);
+ *   topk_w[k] = s[chosen_k] / (sum_k s[chosen_k] + 1e-20) * scale.   outputs <= 1536. */
+int nvllm_moe_route(int32_t* topk_idx, float* topk_w, const float* logits, const float* bias, int32_t n, int32_t outputs,
+                    int32_t top, float scale, void* stream);
+/* Rows the grouped buffers need for n tokens (every expert's segment starts on a 32-row tile). */
+int32_t nvllm_moe_max_rows(int32_t n_tokens, int32_t top, int32_t experts);
+/* Counting sort of the (token, slot) assignments by expert for nvllm_linear_grouped: row_token[max_rows] (token of each
+ * row, -1 padding), tile_expert[max_rows / 32] (-1 unused), slot_row[n * top] (row of each assignment; -1 when it chose an
+ * identity expert, i.e. an index >= experts). */
+int nvllm_moe_sort(int32_t* row_token, int32_t* tile_expert, int32_t* slot_row, const int32_t* topk_idx, int32_t n,
+                   int32_t top, int32_t experts, int32_t max_rows, void* stream);
+/* out[t] = sum_k topk_w[t, k] * (slot_row[t, k] >= 0 ? expert_out[slot_row[t, k]] : x[t]) + shared_out[t] (nullable). */
+int nvllm_moe_combine(void* out, const void* expert_out, const void* x, const void* shared_out, const int32_t* topk_idx,
+                      const float* topk_w, const int32_t* slot_row, int32_t n, int32_t hidden, int32_t top, int32_t experts,
+                      int32_t dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Engine-level C ABI: the C++ host runtime that mirrors the reference's Rust types one-to-one
  * (Config, SamplingParams, Sequence, BlockManager, Scheduler, ModelRunner, Qwen3Model, LLMEngine).
  * Declared in nvllm_engine.h; kept separate so a Rust caller that only wants the kernels binds

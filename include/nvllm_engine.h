@@ -70,7 +70,8 @@ uint64_t nvllm_compute_hash(const int64_t* h_tokens, size_t n, int32_t has_prefi
  * fields of utils/context.rs:11-35 plus ids/positions, as HOST arrays owned by the scheduler (valid until its next
  * schedule call).  i64: seq_ids, input_ids, positions; i32: everything else. */
 typedef struct nvllm_batch {
-  int32_t is_prefill, num_seqs, num_tokens, max_seqlen_q, max_seqlen_k, max_blocks, has_block_tables, reserved;
+  int32_t is_prefill, num_seqs, num_tokens, max_seqlen_q, max_seqlen_k, max_blocks, has_block_tables;
+  int32_t num_logit_rows;      /* length of logit_rows (ignored when logit_rows is NULL) */
   const int64_t* seq_ids;      /* [num_seqs] */
   const int64_t* input_ids;    /* [num_tokens] */
   const int64_t* positions;    /* [num_tokens] */
@@ -82,6 +83,10 @@ typedef struct nvllm_batch {
   const float* temperatures;   /* [num_seqs] */
   const int32_t* top_k;        /* [num_seqs], 0 = None */
   const float* top_p;          /* [num_seqs], 0 = None */
+  /* Prefill-kind batches only, nullable: the tokens of the batch (indices into input_ids) whose logits are computed.
+   * NULL = the last token of every sequence.  With explicit rows, the step's next tokens are chosen from the first
+   * min(num_logit_rows, num_seqs) rows, so a caller that samples lists every sequence's last token first. */
+  const int32_t* logit_rows;
 } nvllm_batch;
 
 /* Scheduler (scheduler.rs:14-334) owning a BlockManager (block_manager.rs:69-331) and the Sequences
@@ -119,11 +124,42 @@ int32_t nvllm_scheduler_sequence(const nvllm_scheduler* s, int64_t seq_id, int64
  * and drops them, llm_engine.rs:186-193).  Its id is never reused; nvllm_scheduler_sequence returns -1 for it afterwards. */
 int nvllm_scheduler_release_sequence(nvllm_scheduler* s, int64_t seq_id);
 
+/* ---- Explicit stepping: the caller names the sequences of a step and how many of their next tokens run — any mix of
+ * prompt portions and single tokens, e.g. to replay a recorded schedule or to stream a prompt in as it arrives.  Blocks
+ * are taken as a sequence grows (fresh ones: no prefix sharing, every position's logits may be asked for) and returned by
+ * nvllm_scheduler_finish_sequence.  A sequence stepped this way stays on this interface until it is finished. */
+/* Appends prompt tokens to a live sequence. */
+int nvllm_scheduler_extend_sequence(nvllm_scheduler* s, int64_t seq_id, const int64_t* h_tokens, int32_t n);
+/* Builds the batch (prefill kind, block tables always present) that runs the next h_counts[i] tokens of sequence
+ * h_seq_ids[i]; fails without side effects when a sequence has fewer tokens left, the step exceeds
+ * max_num_batched_tokens / max_num_seqs, or the cache has too few free blocks. */
+int nvllm_scheduler_schedule_chunks(nvllm_scheduler* s, const int64_t* h_seq_ids, const int32_t* h_counts, int32_t n,
+                                    nvllm_batch* out);
+/* After the step ran: marks the scheduled tokens as present in the cache. */
+int nvllm_scheduler_commit_chunks(nvllm_scheduler* s);
+/* Ends a sequence at any point: its blocks return to the free list (then nvllm_scheduler_release_sequence forgets it). */
+int nvllm_scheduler_finish_sequence(nvllm_scheduler* s, int64_t seq_id);
+
+/* ---- Model registry: architectures beyond the built-in Qwen3 are described by their config.json.  The `architecture`
+ * key of the JSON selects the implementation (nvllm_registered_architectures lists them). */
+const char* nvllm_registered_architectures(void);
+/* Engine defaults (as nvllm_config_init) with vocab_size / hidden_size / num_hidden_layers taken from the model's
+ * configuration; fails when the JSON is malformed or names an unregistered architecture. */
+int nvllm_config_init_for_model(nvllm_config* cfg, const char* model_config_json);
+
 /* ModelRunner (model_runner.rs:19-448) + Qwen3Model (models/qwen3.rs): device weights (this rank's TP shard),
  * per-layer paged KV cache, activation buffers, decode CUDA graphs per batch-size bucket. */
 typedef struct nvllm_runner nvllm_runner;
 int nvllm_runner_create(nvllm_runner** r, const nvllm_config* cfg, nvllm_comm* comm /* NULL when tp == 1 */);
+/* Runner for a registered architecture.  dtype NVLLM_BF16: bf16 operands with f32 accumulation and f32 wherever the
+ * architecture asks for it; NVLLM_F32: weights, activations and cache in true f32 (CUDA-core kernels, no reduced-precision
+ * matrix mode).  Any positive kvcache_block_size; tensor_parallel_size must be 1. */
+int nvllm_runner_create_for_model(nvllm_runner** r, const nvllm_config* cfg, const char* model_config_json, int32_t dtype,
+                                  nvllm_comm* comm);
 int nvllm_runner_destroy(nvllm_runner* r);
+/* Debugging / tests (registered architectures): while h_buf is non-NULL every eager step copies the f32 residual stream
+ * after each layer run to h_buf as [layer runs, tokens of the step, hidden]. */
+int nvllm_runner_layer_tap(nvllm_runner* r, float* h_buf);
 /* Seeded synthetic weights (nvllm_init_weight semantics per logical tensor, sliced per rank; norm weights = 1). */
 int nvllm_runner_init_weights(nvllm_runner* r, uint64_t seed, float std);
 /* Loads one full (unsharded) HF-named tensor from host bf16 memory; the runner keeps its TP slice and packs
@@ -162,6 +198,8 @@ int nvllm_runner_replay_decode(nvllm_runner* r, int32_t iters, float* ms_total);
  * postprocess (llm_engine.rs:155-197).  The async/streaming/tokeniser facade is out of scope. */
 typedef struct nvllm_engine nvllm_engine;
 int nvllm_engine_create(nvllm_engine** e, const nvllm_config* cfg, nvllm_comm* comm);
+int nvllm_engine_create_for_model(nvllm_engine** e, const nvllm_config* cfg, const char* model_config_json, int32_t dtype,
+                                  nvllm_comm* comm);
 int nvllm_engine_destroy(nvllm_engine* e);
 nvllm_scheduler* nvllm_engine_scheduler(nvllm_engine* e);
 nvllm_runner* nvllm_engine_runner(nvllm_engine* e);
@@ -169,6 +207,11 @@ int64_t nvllm_engine_add_request(nvllm_engine* e, const int64_t* h_prompt, int32
 /* One engine step.  out_is_prefill / out_num_seqs / out_num_tokens describe the batch that ran (nullable). */
 int nvllm_engine_step(nvllm_engine* e, int32_t* out_is_prefill, int32_t* out_num_seqs, int32_t* out_num_tokens);
 int nvllm_engine_is_finished(const nvllm_engine* e);
+/* One explicit step: nvllm_scheduler_schedule_chunks -> execute -> nvllm_scheduler_commit_chunks.  h_logit_rows (nullable):
+ * indices into the step's tokens (sequences in the order given, each sequence's tokens in order) whose f32 logits are
+ * written to h_logits [n_rows, vocab]; n_rows == 0 runs the step for its cache only. */
+int nvllm_engine_step_chunks(nvllm_engine* e, const int64_t* h_seq_ids, const int32_t* h_counts, int32_t n,
+                             const int32_t* h_logit_rows, int32_t n_rows, float* h_logits);
 
 #ifdef __cplusplus
 }

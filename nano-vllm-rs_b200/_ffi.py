@@ -77,6 +77,19 @@ PROTOTYPES = {
     "nvllm_gemm_bf16_push": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, vp]),
     "nvllm_allreduce_add_rmsnorm_pushed": (i32, [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp]),
     "nvllm_init_weight": (i32, [vp, i64, u64, u64, f32, i32, vp]),
+    "nvllm_linear": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i64, i64, i64, i32, i32, vp]),
+    "nvllm_linear_grouped": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, vp, vp, i32, f32, i32, i32, vp]),
+    "nvllm_glu_clamped": (i32, [vp, vp, i32, i32, f32, i32, vp]),
+    "nvllm_dyt_residual_norm": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "nvllm_embedding_gather_f32": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "nvllm_gather_rows": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "nvllm_rope_table_interleaved": (i32, [vp, i32, i32, f64, vp]),
+    "nvllm_latent_prepare": (i32, [vp, i64, vp, i64, vp, f32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i64, vp, i32, vp]),
+    "nvllm_latent_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp]),
+    "nvllm_moe_route": (i32, [vp, vp, vp, vp, i32, i32, i32, f32, vp]),
+    "nvllm_moe_max_rows": (i32, [i32, i32, i32]),
+    "nvllm_moe_sort": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "nvllm_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
 }
 
 

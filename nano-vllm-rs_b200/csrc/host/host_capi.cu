@@ -179,6 +179,28 @@ int32_t nvllm_scheduler_sequence(const nvllm_scheduler* s, int64_t seq_id, int64
   return q.len();
 }
 
+int nvllm_scheduler_extend_sequence(nvllm_scheduler* s, int64_t seq_id, const int64_t* h_tokens, int32_t n) {
+  NVLLM_CHECK_ARG(s && n >= 0 && (n == 0 || h_tokens), NVLLM_ERR_ARG, "extend_sequence: arguments");
+  NVLLM_TRY(s->impl.extend_sequence(seq_id, h_tokens, n));
+  return 0;
+}
+int nvllm_scheduler_schedule_chunks(nvllm_scheduler* s, const int64_t* h_seq_ids, const int32_t* h_counts, int32_t n,
+                                    nvllm_batch* out) {
+  NVLLM_CHECK_ARG(s && h_seq_ids && h_counts && out, NVLLM_ERR_ARG, "schedule_chunks: NULL");
+  NVLLM_TRY(s->impl.schedule_chunks(h_seq_ids, h_counts, n, out));
+  return 0;
+}
+int nvllm_scheduler_commit_chunks(nvllm_scheduler* s) {
+  NVLLM_CHECK_ARG(s, NVLLM_ERR_ARG, "commit_chunks: NULL");
+  NVLLM_TRY(s->impl.commit_chunks());
+  return 0;
+}
+int nvllm_scheduler_finish_sequence(nvllm_scheduler* s, int64_t seq_id) {
+  NVLLM_CHECK_ARG(s, NVLLM_ERR_ARG, "finish_sequence: NULL");
+  NVLLM_TRY(s->impl.finish_sequence(seq_id));
+  return 0;
+}
+
 int nvllm_scheduler_release_sequence(nvllm_scheduler* s, int64_t seq_id) {
   NVLLM_CHECK_ARG(s, NVLLM_ERR_ARG, "release_sequence: NULL");
   NVLLM_CHECK_ARG(s->impl.release(seq_id), NVLLM_ERR_STATE, "release_sequence: sequence %lld is unknown or not finished",

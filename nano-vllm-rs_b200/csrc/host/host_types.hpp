@@ -69,6 +69,7 @@ struct Sequence {
   int64_t last_token = 0;
   int32_t num_prompt_tokens = 0;
   int32_t num_cached_tokens = 0;
+  int32_t num_computed_tokens = 0;  // tokens whose cache rows are written (sequences stepped in portions, Scheduler::schedule_chunks)
   std::vector<int32_t> block_table;
   nvllm_sampling_params sp{};
   int32_t block_size = 256;  // follows Config (the reference hard-codes 256, sequence.rs:99)
@@ -161,6 +162,18 @@ class BlockManager {
     }
     s.num_cached_tokens = 0;
     s.block_table.clear();
+  }
+
+  // Sequences that are stepped in portions take their blocks as they go: fresh blocks (no prefix sharing, since every
+  // position's logits may be asked for) until the table covers n_tokens.
+  int32_t blocks_to_grow(const Sequence& s, int32_t n_tokens) const {
+    const int32_t need = (n_tokens + block_size_ - 1) / block_size_ - static_cast<int32_t>(s.block_table.size());
+    return need > 0 ? need : 0;
+  }
+  void grow(Sequence& s, int32_t n_tokens) {
+    const int32_t need = blocks_to_grow(s, n_tokens);
+    if (need > free_count_) throw std::runtime_error("Not enough free blocks to grow sequence");
+    for (int32_t i = 0; i < need; ++i) s.block_table.push_back(take_front());
   }
 
   bool can_append(const Sequence& s) const {                                               // :255-262

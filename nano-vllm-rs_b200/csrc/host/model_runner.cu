@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "../common.cuh"
+#include "model.hpp"
 #include "scheduler.hpp"
 
 namespace nvllm {
@@ -123,6 +124,14 @@ struct nvllm_runner {
   bool fuse_rope = false; // NVLLM_FUSE_ROPE=1: qkv GEMM epilogue does q/k norm + RoPE + KV store for decode-sized batches
   bool fuse_decode = false; // NVLLM_FUSE_DECODE=1 (opt-in, measured slower): q/k-norm + RoPE + KV store inside the paged attention kernel
   bool fused_tp = false;  // h / normed / proj live in NVLink-mapped symmetric memory; all-reduce fused with add + RMSNorm
+  // A registered architecture other than the built-in Qwen3 (model.hpp): owns its weights, cache regions and activations;
+  // the runner keeps the stream, the step metadata, the logits, sampling and the decode graphs.
+  std::unique_ptr<ModelImpl> model;
+  int model_dtype = NVLLM_BF16;
+  int32_t *d_tok_seq = nullptr, *d_logit_rows = nullptr;  // into d_meta: sequence of every token, tokens that feed the head
+  int n_logit_rows = 0, logit_cap = 0;
+  bool explicit_rows = false;
+  float* layer_tap = nullptr;  // host memory (nullable): f32 residual stream after every layer run of eager steps
 
   ~nvllm_runner() {
     for (auto& g : graphs)
@@ -151,6 +160,9 @@ struct nvllm_runner {
   }
 
   int create(const nvllm_config& c, nvllm_comm* cm);
+  int create_for_model(const nvllm_config& c);
+  int forward_model(int n_tokens, int n_seqs);
+  int ensure_logit_rows(int rows);
   int init_weights(uint64_t seed, float std);
   int load_weight(const char* name, const void* h_bf16, int64_t rows, int64_t cols);
   int upload(const nvllm_batch& b, int padded);
@@ -188,7 +200,74 @@ static int bucket_for(int b, int max_seqs) {
   return p > max_seqs ? max_seqs : p;
 }
 
+// Runner around a registered model: the model allocates what it needs; the runner sizes the step metadata for any mix of
+// prompt portions and single tokens (every step carries block tables, a per-token sequence index and the logit rows).
+int nvllm_runner::create_for_model(const nvllm_config& c) {
+  NVLLM_CHECK_ARG(nvllm_device_ok() == 1, NVLLM_ERR_STATE, "runner_create: no sm_100 CUDA device (there is no CPU path)");
+  NVLLM_CHECK_ARG(c.tensor_parallel_size == 1, NVLLM_ERR_ARG, "runner_create: this architecture runs on one GPU (tensor_parallel_size 1)");
+  NVLLM_CHECK_ARG(c.kvcache_block_size > 0 && c.max_num_seqs > 0 && c.max_num_batched_tokens > 0 && c.max_model_len > 0 &&
+                      c.num_kvcache_blocks >= 0, NVLLM_ERR_ARG, "runner_create: block size / limits must be positive");
+  cfg = c;
+  tp = 1; rank = 0;
+  vocab = vshard = model->vocab();
+  hidden = model->hidden();
+  layers = model->layer_runs();
+  max_seqs = c.max_num_seqs;
+  max_tokens = c.max_num_batched_tokens > max_seqs ? c.max_num_batched_tokens : max_seqs;
+  num_blocks = c.num_kvcache_blocks > 0 ? c.num_kvcache_blocks : 1000;
+  const int bs = c.kvcache_block_size;
+  table_cap = (c.max_model_len + bs - 1) / bs;
+  layout.block_size = bs;
+  NVLLM_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  ModelLimits lim;
+  lim.max_tokens = max_tokens; lim.max_seqs = max_seqs; lim.num_blocks = num_blocks; lim.block_size = bs;
+  lim.table_cap = table_cap; lim.max_positions = c.max_model_len + 1; lim.dtype = model_dtype;
+  RUN(model->create(lim, stream));
+  RUN(ensure_logit_rows(max_seqs));
+  RUN(dalloc(&tokens, max_seqs));
+  const size_t T = max_tokens, S = max_seqs;
+  const size_t prefill_meta = 28 * T + 8 * (S + 1) + 4 * S * table_cap;
+  const size_t decode_meta = S * (32 + 4 * static_cast<size_t>(table_cap));
+  meta_bytes = (prefill_meta > decode_meta ? prefill_meta : decode_meta) + 64;
+  RUN(dalloc(&d_meta, meta_bytes));
+  NVLLM_CUDA(cudaMallocHost(reinterpret_cast<void**>(&h_meta), meta_bytes));
+  NVLLM_CUDA(cudaMallocHost(reinterpret_cast<void**>(&h_tokens), sizeof(int64_t) * S));
+  RUN(dalloc(&d_samp, 24 * S));
+  NVLLM_CUDA(cudaMallocHost(reinterpret_cast<void**>(&h_samp), 24 * S));
+  NVLLM_CUDA(cudaStreamSynchronize(stream));
+  return 0;
+}
+
+// The logits buffer grows with the number of rows a step asks for (never inside a graph capture: captured decode steps
+// ask for one row per sequence, which the initial size covers).
+int nvllm_runner::ensure_logit_rows(int rows) {
+  if (rows <= logit_cap) return 0;
+  NVLLM_CUDA(cudaStreamSynchronize(stream));
+  RUN(dalloc(&logits, static_cast<size_t>(rows) * vshard));
+  logit_cap = rows;
+  return 0;
+}
+
+int nvllm_runner::forward_model(int N, int S) {
+  StepView v;
+  v.stream = stream; v.n_tokens = N; v.n_seqs = S;
+  v.ids = d_ids; v.positions = d_pos; v.slots = d_slots; v.tok_seq = d_tok_seq; v.tables = d_tables; v.table_cap = table_cap;
+  v.logit_rows = d_logit_rows; v.n_logit_rows = n_logit_rows; v.logits = logits;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  v.capturing = cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone;
+  v.layer_tap = layer_tap;
+  mark("(step start)");
+  RUN(model->forward(v));
+  launches = model->launches;
+  mark("model forward");
+  // next-token choice from the first min(rows, seqs) logit rows (by default row i is the last token of sequence i)
+  const int rows = n_logit_rows < S ? n_logit_rows : S;
+  if (rows > 0) { RUN(nvllm_argmax(tokens, nullptr, logits, rows, vshard, vshard, 0, NVLLM_F32, stream)); ++launches; mark("argmax"); }
+  return 0;
+}
+
 int nvllm_runner::create(const nvllm_config& c, nvllm_comm* cm) {
+  if (model) return create_for_model(c);
   RUN(nvllm_config_validate(&c));
   NVLLM_CHECK_ARG(nvllm_device_ok() == 1, NVLLM_ERR_STATE, "runner_create: no sm_100 CUDA device (there is no CPU path)");
   cfg = c;
@@ -263,6 +342,7 @@ int nvllm_runner::create(const nvllm_config& c, nvllm_comm* cm) {
   RUN(dalloc(&gate_up, T * 2 * inter)); RUN(dalloc(&act, T * inter));
   RUN(dalloc(&last_hidden, static_cast<size_t>(max_seqs) * hidden));
   RUN(dalloc(&logits, static_cast<size_t>(max_seqs) * vshard));
+  logit_cap = max_seqs;
   // gathered_logits / full_logits (tp > 1, 2 x max_seqs x vocab f32 = 2 x 311 MB at 512 x 151936) are taken on the first
   // SAMPLED batch (sample() below): greedy-only serving, the benchmarked TP configuration included, never pays for them.
   RUN(dalloc(&tokens, max_seqs)); RUN(dalloc(&local_ids, max_seqs)); RUN(dalloc(&local_max, max_seqs));
@@ -278,8 +358,8 @@ int nvllm_runner::create(const nvllm_config& c, nvllm_comm* cm) {
   if (decode_ws_bytes) { uint8_t* p = nullptr; RUN(dalloc(&p, decode_ws_bytes)); decode_ws = p; }
   // metadata
   const size_t S = max_seqs;
-  const size_t prefill_meta = 20 * T + 8 * (S + 1) + 4 * S * table_cap;
-  const size_t decode_meta = S * (24 + 4 * static_cast<size_t>(table_cap));
+  const size_t prefill_meta = 28 * T + 8 * (S + 1) + 4 * S * table_cap;
+  const size_t decode_meta = S * (32 + 4 * static_cast<size_t>(table_cap));
   meta_bytes = (prefill_meta > decode_meta ? prefill_meta : decode_meta) + 64;
   RUN(dalloc(&d_meta, meta_bytes));
   NVLLM_CUDA(cudaMallocHost(reinterpret_cast<void**>(&h_meta), meta_bytes));
@@ -294,6 +374,11 @@ int nvllm_runner::create(const nvllm_config& c, nvllm_comm* cm) {
 // Logical tensor ids of the seeded init (mirrored by oracle/qwen3.py): 1 embed, 2 lm_head, 16*(l+1) + {0 q, 1 k,
 // 2 v, 3 o, 4 gate, 5 up, 6 down}.  Norm weights are 1.
 int nvllm_runner::init_weights(uint64_t seed, float std) {
+  if (model) {
+    RUN(model->init_weights(seed, std, stream));
+    weights_ready = model->weights_ready();
+    return 0;
+  }
   const float scale = std * 2.6428998e-05f;
   auto shard = [&](bf16* dst, int64_t rows, int64_t cols, int64_t ld, int64_t full_cols, int64_t row0, int64_t col0,
                    uint64_t id) {
@@ -339,6 +424,11 @@ int nvllm_runner::init_weights(uint64_t seed, float std) {
 // HF tensor names -> this rank's slice (utils/loader.rs:175-198 packed-module mapping; linear.rs:154-172,249-267).
 int nvllm_runner::load_weight(const char* name_c, const void* src, int64_t rows, int64_t cols) {
   NVLLM_CHECK_ARG(name_c && src, NVLLM_ERR_ARG, "load_weight: NULL");
+  if (model) {
+    RUN(model->load_weight(name_c, src, rows, cols, stream));
+    weights_ready = model->weights_ready();
+    return 0;
+  }
   const std::string name(name_c);
   const int Hf = cfg.num_attention_heads, Hkvf = cfg.num_key_value_heads, If = cfg.intermediate_size;
   // copies rows [r0, r0+nr) x cols [c0, c0+nc) of the host tensor (pitch `cols`) into dst (pitch nc)
@@ -412,13 +502,37 @@ int nvllm_runner::upload(const nvllm_batch& b, int padded) {
     d_cu_k = reinterpret_cast<int32_t*>(d_meta + put(b.cu_seqlens_k, 4 * (S + 1)));
     d_ctx = nullptr;
     d_tables = nullptr;
-    if (b.has_block_tables) {
+    // a registered model reads every step through the block tables; the built-in Qwen3 only when a prefix is cached
+    if (b.has_block_tables || (model && b.block_tables != nullptr)) {
       NVLLM_CHECK_ARG(static_cast<size_t>(b.max_blocks) <= cap, NVLLM_ERR_ARG, "execute: block table wider than max_model_len allows");
       d_tables = reinterpret_cast<int32_t*>(d_meta + o);
       int32_t* t = reinterpret_cast<int32_t*>(h_meta + o);
       for (size_t i = 0; i < S; ++i)
         for (size_t j = 0; j < cap; ++j) t[i * cap + j] = j < static_cast<size_t>(b.max_blocks) ? b.block_tables[i * b.max_blocks + j] : -1;
       o += 4 * S * cap;
+    }
+    {  // sequence of every token, and the tokens whose logits are wanted (default: the last token of every sequence)
+      int32_t* ts = reinterpret_cast<int32_t*>(h_meta + o);
+      d_tok_seq = reinterpret_cast<int32_t*>(d_meta + o);
+      for (size_t i = 0; i < S; ++i)
+        for (int32_t t = b.cu_seqlens_q[i]; t < b.cu_seqlens_q[i + 1]; ++t) ts[t] = static_cast<int32_t>(i);
+      o += 4 * N;
+      int32_t* lr = reinterpret_cast<int32_t*>(h_meta + o);
+      d_logit_rows = reinterpret_cast<int32_t*>(d_meta + o);
+      explicit_rows = b.logit_rows != nullptr;
+      if (explicit_rows) {
+        NVLLM_CHECK_ARG(b.num_logit_rows >= 0 && static_cast<size_t>(b.num_logit_rows) <= N, NVLLM_ERR_ARG,
+                        "execute: %d logit rows for %zu tokens", b.num_logit_rows, N);
+        n_logit_rows = b.num_logit_rows;
+        for (int i = 0; i < n_logit_rows; ++i) {
+          NVLLM_CHECK_ARG(b.logit_rows[i] >= 0 && static_cast<size_t>(b.logit_rows[i]) < N, NVLLM_ERR_ARG, "execute: logit row %d out of range", b.logit_rows[i]);
+          lr[i] = b.logit_rows[i];
+        }
+      } else {
+        n_logit_rows = static_cast<int>(S);
+        for (size_t i = 0; i < S; ++i) lr[i] = b.cu_seqlens_q[i + 1] - 1;
+      }
+      o += 4 * static_cast<size_t>(n_logit_rows);
     }
     used = o;
   } else {
@@ -446,6 +560,15 @@ int nvllm_runner::upload(const nvllm_batch& b, int padded) {
     d_tables = reinterpret_cast<int32_t*>(d_meta + 24 * P);
     d_cu_q = d_cu_k = nullptr;
     used = P * (24 + 4 * cap);
+    {  // one token per sequence: token i belongs to sequence i and feeds logit row i
+      int32_t* ts = reinterpret_cast<int32_t*>(h_meta + used);
+      d_tok_seq = reinterpret_cast<int32_t*>(d_meta + used);
+      d_logit_rows = d_tok_seq + P;
+      for (size_t i = 0; i < P; ++i) ts[i] = ts[P + i] = static_cast<int32_t>(i);
+      used += 8 * P;
+      n_logit_rows = static_cast<int>(P);
+      explicit_rows = false;
+    }
     last_decode_b = static_cast<int>(P);
     last_ctx.assign(ctx, ctx + P);
   }
@@ -457,6 +580,7 @@ int nvllm_runner::upload(const nvllm_batch& b, int padded) {
 // Qwen3Model::forward (qwen3.rs:487-505) -> Qwen3Layer::forward (:372-392) -> Qwen3Attention::forward (:208-240) /
 // Qwen3MLP::forward (:305-314) -> ParallelLMHead::forward (embed_head.rs:250-269) -> greedy sample (sampler.rs:109-112).
 int nvllm_runner::forward(int N, int S, bool is_prefill, bool paged_prefill, const nvllm_batch& b) {
+  if (model) return forward_model(N, S);
   void* st = stream;
   const float eps = cfg.rms_norm_eps;
   const float scale = 1.0f / sqrtf(static_cast<float>(D));  // attention.rs:45
@@ -554,7 +678,12 @@ int nvllm_runner::forward(int N, int S, bool is_prefill, bool paged_prefill, con
   RUN(add_norm(final_norm));                                                                                           // qwen3.rs:389,501
   const bf16* head_in = normed;
   int rows = N;
-  if (is_prefill) {  // only the last token of each sequence feeds the head (embed_head.rs:250-289)
+  if (is_prefill && explicit_rows) {  // the caller named the tokens whose logits it wants
+    NVLLM_CHECK_ARG(n_logit_rows > 0 && n_logit_rows <= max_seqs, NVLLM_ERR_ARG, "execute: %d logit rows (1..max_num_seqs for this architecture)", n_logit_rows);
+    RUN(nvllm_gather_rows(last_hidden, normed, d_logit_rows, n_logit_rows, hidden, N, NVLLM_BF16, st)); ++launches; mark("gather_rows");
+    head_in = last_hidden;
+    rows = n_logit_rows;
+  } else if (is_prefill) {  // only the last token of each sequence feeds the head (embed_head.rs:250-289)
     RUN(nvllm_gather_last_tokens(last_hidden, normed, d_cu_q, S, hidden, NVLLM_BF16, st)); ++launches; mark("gather_last_tokens");
     head_in = last_hidden;
     rows = S;
@@ -583,6 +712,7 @@ int nvllm_runner::execute_async(const nvllm_batch& b) {
   for (int i = 0; i < b.num_seqs && b.temperatures != nullptr; ++i) sampled |= b.temperatures[i] != 0.0f;
   if (b.is_prefill) {
     RUN(upload(b, 0));
+    if (model) RUN(ensure_logit_rows(n_logit_rows));
     RUN(forward(b.num_tokens, b.num_seqs, true, b.has_block_tables != 0, b));
     last_launches = launches;
   } else {
@@ -691,6 +821,49 @@ int nvllm_runner_create(nvllm_runner** r, const nvllm_config* cfg, nvllm_comm* c
   *r = p;
   return 0;
 }
+int nvllm_runner_create_for_model(nvllm_runner** r, const nvllm_config* cfg, const char* model_config_json, int32_t dtype,
+                                  nvllm_comm* comm) {
+  NVLLM_CHECK_ARG(r && cfg && model_config_json, NVLLM_ERR_ARG, "runner_create_for_model: NULL");
+  NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "runner_create_for_model: dtype %d", dtype);
+  nvllm_runner* p = nullptr;
+  NVLLM_TRY_NEW(p, new nvllm_runner());
+  ModelImpl* m = nullptr;
+  try {
+    m = make_model(json::parse(model_config_json));
+  } catch (const std::exception& e) {
+    set_error("%s", e.what());
+  }
+  if (m == nullptr) { delete p; return NVLLM_ERR_ARG; }
+  p->model.reset(m);
+  p->model_dtype = dtype;
+  const int rc = p->create(*cfg, comm);
+  if (rc != 0) { delete p; return rc; }
+  *r = p;
+  return 0;
+}
+int nvllm_runner_layer_tap(nvllm_runner* r, float* h_buf) {
+  NVLLM_CHECK_ARG(r, NVLLM_ERR_ARG, "runner_layer_tap: NULL");
+  NVLLM_CUDA(cudaStreamSynchronize(r->stream));
+  r->layer_tap = h_buf;
+  return 0;
+}
+const char* nvllm_registered_architectures(void) { return registered_architectures(); }
+int nvllm_config_init_for_model(nvllm_config* cfg, const char* model_config_json) {
+  NVLLM_CHECK_ARG(cfg && model_config_json, NVLLM_ERR_ARG, "config_init_for_model: NULL");
+  RUN(nvllm_config_init(cfg, "tiny"));
+  std::unique_ptr<ModelImpl> m;
+  try {
+    m.reset(make_model(json::parse(model_config_json)));
+  } catch (const std::exception& e) {
+    set_error("%s", e.what());
+  }
+  if (!m) return NVLLM_ERR_ARG;
+  cfg->vocab_size = m->vocab(); cfg->hidden_size = m->hidden(); cfg->num_hidden_layers = m->layer_runs();
+  // the Qwen3-only fields carry no meaning for a registered architecture
+  cfg->intermediate_size = 0; cfg->num_attention_heads = 0; cfg->num_key_value_heads = 0; cfg->head_dim = 0;
+  cfg->qk_norm = 0; cfg->tie_word_embeddings = 0; cfg->max_position_embeddings = cfg->max_model_len;
+  return 0;
+}
 int nvllm_runner_destroy(nvllm_runner* r) {
   if (r) { cudaStreamSynchronize(r->stream); delete r; }
   return 0;
@@ -714,8 +887,9 @@ int nvllm_runner_fetch_tokens(nvllm_runner* r, int64_t* h_tokens, int32_t n) {
 int nvllm_runner_execute(nvllm_runner* r, const nvllm_batch* b, int64_t* h_tokens, float* h_logits) {
   NVLLM_CHECK_ARG(r && b, NVLLM_ERR_ARG, "runner_execute: NULL");
   RUN(r->execute_async(*b));
-  if (h_logits)
-    NVLLM_CUDA(cudaMemcpyAsync(h_logits, r->logits, sizeof(float) * b->num_seqs * r->vshard, cudaMemcpyDeviceToHost, r->stream));
+  const size_t logit_rows = (b->is_prefill && r->explicit_rows) ? r->n_logit_rows : b->num_seqs;
+  if (h_logits && logit_rows > 0)
+    NVLLM_CUDA(cudaMemcpyAsync(h_logits, r->logits, sizeof(float) * logit_rows * r->vshard, cudaMemcpyDeviceToHost, r->stream));
   return r->fetch(h_tokens, b->num_seqs);
 }
 void* nvllm_runner_stream(nvllm_runner* r) { return r ? r->stream : nullptr; }
@@ -744,6 +918,7 @@ int64_t nvllm_runner_profile_report(nvllm_runner* r, char* h_buf, size_t cap) {
 }
 int64_t nvllm_runner_last_launches(const nvllm_runner* r) { return r ? r->last_launches : 0; }
 int nvllm_runner_kv_cache(nvllm_runner* r, int32_t layer, void** k_cache, void** v_cache, nvllm_kv_layout* layout) {
+  NVLLM_CHECK_ARG(r && !r->model, NVLLM_ERR_STATE, "runner_kv_cache: built-in Qwen3 runner only");
   NVLLM_CHECK_ARG(r && layer >= 0 && layer < r->layers, NVLLM_ERR_ARG, "runner_kv_cache: layer %d", layer);
   if (k_cache) *k_cache = r->kc[layer];
   if (v_cache) *v_cache = r->vc[layer];
@@ -781,6 +956,7 @@ int nvllm_runner_replay_decode(nvllm_runner* r, int32_t iters, float* ms_total) 
 // layers' caches so that consecutive launches never re-read the same KV from L2; CUDA events on the runner's stream.
 int nvllm_runner_time_decode_attention(nvllm_runner* r, int32_t iters, float* ms_per_launch, int64_t* alg_bytes) {
   NVLLM_CHECK_ARG(r && iters > 0 && ms_per_launch, NVLLM_ERR_ARG, "time_decode_attention: arguments");
+  NVLLM_CHECK_ARG(!r->model, NVLLM_ERR_STATE, "time_decode_attention: built-in Qwen3 runner only");
   NVLLM_CHECK_ARG(r->last_decode_b > 0 && r->d_ctx != nullptr, NVLLM_ERR_STATE, "time_decode_attention: no decode step has run yet");
   const int B = r->last_decode_b, HD = r->H * r->D;
   const float scale = 1.0f / sqrtf(static_cast<float>(r->D));
@@ -852,6 +1028,33 @@ int nvllm_engine_create(nvllm_engine** e, const nvllm_config* cfg, nvllm_comm* c
   p->toks.resize(cfg->max_num_seqs);
   *e = p;
   return 0;
+}
+int nvllm_engine_create_for_model(nvllm_engine** e, const nvllm_config* cfg, const char* model_config_json, int32_t dtype,
+                                  nvllm_comm* comm) {
+  NVLLM_CHECK_ARG(e && cfg && model_config_json, NVLLM_ERR_ARG, "engine_create_for_model: NULL");
+  nvllm_engine* p = nullptr;
+  NVLLM_TRY_NEW(p, new nvllm_engine());
+  int rc = nvllm_scheduler_create(&p->sched, cfg);
+  if (rc == 0) rc = nvllm_runner_create_for_model(&p->runner, cfg, model_config_json, dtype, comm);
+  if (rc != 0) {
+    if (p->sched) nvllm_scheduler_destroy(p->sched);
+    delete p;
+    return rc;
+  }
+  p->toks.resize(cfg->max_num_seqs);
+  *e = p;
+  return 0;
+}
+int nvllm_engine_step_chunks(nvllm_engine* e, const int64_t* h_seq_ids, const int32_t* h_counts, int32_t n,
+                             const int32_t* h_logit_rows, int32_t n_rows, float* h_logits) {
+  NVLLM_CHECK_ARG(e && n_rows >= 0 && (n_rows == 0 || (h_logit_rows && h_logits)), NVLLM_ERR_ARG, "engine_step_chunks: arguments");
+  nvllm_batch b;
+  RUN(nvllm_scheduler_schedule_chunks(e->sched, h_seq_ids, h_counts, n, &b));
+  static const int32_t none = 0;
+  b.logit_rows = n_rows > 0 ? h_logit_rows : &none;  // explicit (possibly empty) row list
+  b.num_logit_rows = n_rows;
+  RUN(nvllm_runner_execute(e->runner, &b, e->toks.data(), n_rows > 0 ? h_logits : nullptr));
+  return nvllm_scheduler_commit_chunks(e->sched);
 }
 int nvllm_engine_destroy(nvllm_engine* e) {
   if (!e) return 0;

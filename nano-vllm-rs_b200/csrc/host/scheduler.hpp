@@ -75,6 +75,102 @@ class Scheduler {
     return true;
   }
 
+  // ---- explicit stepping: the caller names the sequences of a step and how many of their next tokens run ----------
+  // A serving loop that replays a recorded schedule, or a front end that streams a prompt in as it arrives, decides the
+  // batches itself: any mix of prompt portions and single tokens.  Prompt tokens may be appended to a live sequence;
+  // blocks are taken as the sequence grows and given back by finish_sequence.
+  void extend_sequence(int64_t seq_id, const int64_t* toks, int32_t n) {
+    auto it = id_to_slot_.find(seq_id);
+    if (it == id_to_slot_.end() || seqs_[it->second].status == Status::Finished)
+      throw std::invalid_argument("extend_sequence: sequence " + std::to_string(seq_id) + " is unknown or finished");
+    Sequence& s = seqs_[it->second];
+    if (max_model_len_ > 0 && s.len() + n > max_model_len_)
+      throw std::invalid_argument("extend_sequence: sequence would exceed max_model_len " + std::to_string(max_model_len_));
+    s.token_ids.insert(s.token_ids.end(), toks, toks + n);
+    s.num_prompt_tokens += n;
+    if (n > 0) s.last_token = toks[n - 1];
+  }
+
+  void schedule_chunks(const int64_t* seq_ids, const int32_t* counts, int32_t n, nvllm_batch* out) {
+    if (n <= 0 || n > max_num_seqs_) throw std::invalid_argument("schedule_chunks: 1..max_num_seqs sequences per step");
+    std::vector<int32_t> slots(n);
+    int64_t total = 0, need_blocks = 0;
+    for (int32_t i = 0; i < n; ++i) {  // validate everything before any state changes
+      auto it = id_to_slot_.find(seq_ids[i]);
+      if (it == id_to_slot_.end() || seqs_[it->second].status == Status::Finished)
+        throw std::invalid_argument("schedule_chunks: sequence " + std::to_string(seq_ids[i]) + " is unknown or finished");
+      for (int32_t j = 0; j < i; ++j)
+        if (slots[j] == it->second) throw std::invalid_argument("schedule_chunks: a sequence is listed twice");
+      slots[i] = it->second;
+      const Sequence& s = seqs_[it->second];
+      if (counts[i] <= 0 || s.num_computed_tokens + counts[i] > s.len())
+        throw std::invalid_argument("schedule_chunks: sequence " + std::to_string(seq_ids[i]) + " has " +
+                                    std::to_string(s.len() - s.num_computed_tokens) + " tokens left, asked for " + std::to_string(counts[i]));
+      total += counts[i];
+      need_blocks += bm_.blocks_to_grow(s, s.num_computed_tokens + counts[i]);
+    }
+    if (total > max_num_batched_tokens_) throw std::invalid_argument("schedule_chunks: step exceeds max_num_batched_tokens");
+    if (need_blocks > bm_.num_free()) throw std::runtime_error("schedule_chunks: not enough free cache blocks");
+    arrays_.seq_index.assign(slots.begin(), slots.end());
+    chunk_counts_.assign(counts, counts + n);
+    for (int32_t i = 0; i < n; ++i) {
+      Sequence& s = seqs_[slots[i]];
+      if (s.status != Status::Running) {
+        waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), slots[i]), waiting_.end());
+        s.status = Status::Running;
+        running_.push_back(slots[i]);
+      }
+      bm_.grow(s, s.num_computed_tokens + counts[i]);
+    }
+    ++prefill_batches_;
+    fill_common(out, true);
+    BatchArrays& a = arrays_;
+    a.input_ids.clear(); a.positions.clear(); a.slot_mapping.clear();
+    a.cu_q.assign(1, 0); a.cu_k.assign(1, 0);
+    int32_t max_q = 0, max_k = 0;
+    for (int32_t i = 0; i < n; ++i) {
+      const Sequence& s = seqs_[slots[i]];
+      const int32_t start = s.num_computed_tokens, end = start + counts[i];
+      for (int32_t p = start; p < end; ++p) {
+        a.input_ids.push_back(s.token_ids[p]);
+        a.positions.push_back(p);
+        a.slot_mapping.push_back(s.block_table[p / block_size_] * block_size_ + p % block_size_);
+      }
+      a.cu_q.push_back(a.cu_q.back() + counts[i]);
+      a.cu_k.push_back(a.cu_k.back() + end);
+      max_q = std::max(max_q, counts[i]);
+      max_k = std::max(max_k, end);
+    }
+    out->num_tokens = static_cast<int32_t>(a.input_ids.size());
+    out->input_ids = a.input_ids.data(); out->positions = a.positions.data();
+    out->slot_mapping = a.slot_mapping.data();
+    out->cu_seqlens_q = a.cu_q.data(); out->cu_seqlens_k = a.cu_k.data();
+    out->max_seqlen_q = max_q; out->max_seqlen_k = max_k;
+    fill_tables(out);
+  }
+
+  // After the step ran: the scheduled tokens are in the cache.
+  void commit_chunks() {
+    if (chunk_counts_.size() != arrays_.seq_index.size()) throw std::runtime_error("commit_chunks: no portion step is pending");
+    for (size_t i = 0; i < chunk_counts_.size(); ++i) seqs_[arrays_.seq_index[i]].num_computed_tokens += chunk_counts_[i];
+    chunk_counts_.clear();
+    arrays_.seq_index.clear();
+  }
+
+  void finish_sequence(int64_t seq_id) {
+    auto it = id_to_slot_.find(seq_id);
+    if (it == id_to_slot_.end() || seqs_[it->second].status == Status::Finished)
+      throw std::invalid_argument("finish_sequence: sequence " + std::to_string(seq_id) + " is unknown or finished");
+    const int32_t si = it->second;
+    Sequence& s = seqs_[si];
+    s.status = Status::Finished;
+    if (!s.block_table.empty()) bm_.deallocate(s);
+    s.num_computed_tokens = 0;
+    running_.erase(std::remove(running_.begin(), running_.end(), si), running_.end());
+    waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), si), waiting_.end());
+    ++finished_;
+  }
+
   // Scheduler::schedule (:103-116): prefill first, else decode.  Fills `out` (pointers into arrays_).
   void schedule(nvllm_batch* out) {
     arrays_.seq_index.clear();
@@ -235,7 +331,10 @@ class Scheduler {
     out->slot_mapping = a.slot_mapping.data();
     out->cu_seqlens_q = a.cu_q.data(); out->cu_seqlens_k = a.cu_k.data();
     out->max_seqlen_q = max_q; out->max_seqlen_k = max_k;
-    if (any_cached) fill_tables(out);
+    // the tables always travel (architectures whose attention reads every step through the paged cache need them);
+    // has_block_tables keeps its meaning: some sequence of the batch starts behind a cached prefix
+    fill_tables(out);
+    if (!any_cached) out->has_block_tables = 0;
   }
 
   // prepare_decode_inputs + create_decode_context (model_runner.rs:196-210,266-300)
@@ -267,6 +366,7 @@ class Scheduler {
   int64_t next_seq_id_ = 0;
   std::deque<int32_t> waiting_, running_;
   BatchArrays arrays_;
+  std::vector<int32_t> chunk_counts_;  // tokens per sequence of the pending portion step (schedule_chunks -> commit_chunks)
   int64_t total_sequences_ = 0, finished_ = 0, preemptions_ = 0, prefill_batches_ = 0, decode_batches_ = 0;
 };
 

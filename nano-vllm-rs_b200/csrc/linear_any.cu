@@ -1,0 +1,195 @@
+// linear_any.cu — y = x . w^T for ANY sizes, strides, batch counts and for bf16 or f32 operands (nvllm_linear), plus the
+// grouped / gathered variants a mixture-of-experts layer needs (nvllm_linear_grouped) and the gated pair with its
+// activation in the epilogue (GLU).  Dense bf16 problems whose shapes meet the tensor-core kernel's rules (k % 64, n % 8,
+// 16-byte rows) are forwarded to nvllm_gemm_bf16 (tcgen05); everything else — odd sizes, per-head batches, expert groups,
+// true 32-bit models — runs on the CUDA-core tile kernel below: 32 x 64 output tile, 32-wide k steps staged in shared
+// memory as f32, f32 accumulation in ascending k order, so a row's result never depends on which other rows are in the
+// batch.
+#include "common.cuh"
+
+namespace nvllm {
+namespace {
+
+struct LinArgs {
+  void* y; const void* x; const void* w;
+  int M, N, K;
+  int64_t ldx, ldw, ldy, bsx, bsw, bsy;
+  const int32_t* row_src;     // gathered rows of x (row i of the problem reads x[row_src[i]]; < 0 = zero row, not written)
+  const int32_t* tile_group;  // group (expert) of every 32-row tile; < 0 = tile unused.  w += group * bsw
+  int64_t up_off;             // GLU: element offset of the `up` rows relative to the `gate` rows inside w
+  float limit;                // GLU clamp
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int BM = 32, BN = 64, BK = 32;
+
+// GLU epilogue of the gated feed-forward used by the mixture-of-experts layers:
+//   g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float glu_clamped(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+}
+
+template <typename TI, typename TO, bool GLU>
+__global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
+  __shared__ float xs[BM][BK + 1];
+  __shared__ float ws[BN][BK + 1];
+  __shared__ float us[GLU ? BN : 1][BK + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  int group = 0;
+  if (a.tile_group != nullptr) {
+    group = a.tile_group[blockIdx.y];
+    if (group < 0) return;
+  }
+  const int b = blockIdx.z;
+  const TI* x = static_cast<const TI*>(a.x) + b * a.bsx;
+  const TI* w = static_cast<const TI*>(a.w) + (b + group) * a.bsw;
+  TO* y = static_cast<TO*>(a.y) + b * a.bsy;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[2][4], acu[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = acu[i][j] = 0.f;
+  // each thread stages 4 elements of x and 8 (16 with GLU) of w per k step: row = e / BK, col = e % BK
+  for (int k0 = 0; k0 < a.K; k0 += BK) {
+#pragma unroll
+    for (int e = tid; e < BM * BK; e += 256) {
+      const int r = e / BK, c = e % BK, m = m0 + r, k = k0 + c;
+      float v = 0.f;
+      if (m < a.M && k < a.K) {
+        const int64_t src = a.row_src ? a.row_src[m] : m;
+        if (src >= 0) v = ldf(x + src * a.ldx + k);
+      }
+      xs[r][c] = v;
+    }
+#pragma unroll
+    for (int e = tid; e < BN * BK; e += 256) {
+      const int r = e / BK, c = e % BK, n = n0 + r, k = k0 + c;
+      const bool ok = n < a.N && k < a.K;
+      ws[r][c] = ok ? ldf(w + static_cast<int64_t>(n) * a.ldw + k) : 0.f;
+      if (GLU) us[r][c] = ok ? ldf(w + a.up_off + static_cast<int64_t>(n) * a.ldw + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int kk = 0; kk < BK; ++kk) {
+      const float x0 = xs[ty * 2][kk], x1 = xs[ty * 2 + 1][kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float wv = ws[tx + 16 * j][kk];
+        acc[0][j] = fmaf(x0, wv, acc[0][j]);
+        acc[1][j] = fmaf(x1, wv, acc[1][j]);
+        if (GLU) {
+          const float uv = us[tx + 16 * j][kk];
+          acu[0][j] = fmaf(x0, uv, acu[0][j]);
+          acu[1][j] = fmaf(x1, uv, acu[1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = m0 + ty * 2 + i;
+    if (m >= a.M || (a.row_src && a.row_src[m] < 0)) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n >= a.N) continue;
+      float v = acc[i][j];
+      if (GLU) {
+        // bf16 models round gate and up to bf16 before the activation, as a separate projection would have
+        float g = v, u = acu[i][j];
+        if (sizeof(TI) == 2) { g = __bfloat162float(__float2bfloat16_rn(g)); u = __bfloat162float(__float2bfloat16_rn(u)); }
+        v = glu_clamped(g, u, a.limit);
+      }
+      stf(y + static_cast<int64_t>(m) * a.ldy + n, v);
+    }
+  }
+}
+
+template <typename T>
+__global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int64_t n, int ff, float limit) {
+  const int64_t total = n * ff;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / ff, c = i - r * ff;
+    stf(out + i, glu_clamped(ldf(gate_up + r * 2 * ff + c), ldf(gate_up + r * 2 * ff + ff + c), limit));
+  }
+}
+
+template <bool GLU>
+int launch_tile(const LinArgs& a, int m_tiles, int batch, int dtype, int out_dtype, cudaStream_t st) {
+  dim3 grid((a.N + BN - 1) / BN, m_tiles, batch);
+  if (dtype == NVLLM_BF16 && out_dtype == NVLLM_BF16) linear_tile_kernel<bf16, bf16, GLU><<<grid, 256, 0, st>>>(a);
+  else if (dtype == NVLLM_BF16) linear_tile_kernel<bf16, float, GLU><<<grid, 256, 0, st>>>(a);
+  else if (out_dtype == NVLLM_F32) linear_tile_kernel<float, float, GLU><<<grid, 256, 0, st>>>(a);
+  else { set_error("linear: f32 operands need an f32 output"); return NVLLM_ERR_DTYPE; }
+  NVLLM_LAUNCH_CHECK("linear_tile_kernel");
+  return 0;
+}
+
+}  // namespace
+}  // namespace nvllm
+
+using namespace nvllm;
+
+extern "C" int nvllm_linear(void* y, const void* x, const void* w, int32_t m, int32_t n, int32_t k, int64_t ldx, int64_t ldw,
+                            int64_t ldy, int32_t batch, int64_t bsx, int64_t bsw, int64_t bsy, int32_t dtype,
+                            int32_t out_dtype, void* stream) {
+  NVLLM_CHECK_ARG(m >= 0 && n > 0 && k > 0 && batch > 0, NVLLM_ERR_ARG, "linear: m=%d n=%d k=%d batch=%d", m, n, k, batch);
+  NVLLM_CHECK_ARG(ldx >= k && ldw >= k && ldy >= n, NVLLM_ERR_ARG, "linear: leading dimensions");
+  NVLLM_CHECK_ARG((dtype == NVLLM_BF16 || dtype == NVLLM_F32) && (out_dtype == NVLLM_BF16 || out_dtype == NVLLM_F32),
+                  NVLLM_ERR_DTYPE, "linear: dtype %d / %d", dtype, out_dtype);
+  if (m == 0) return 0;
+  NVLLM_CHECK_ARG(y && x && w, NVLLM_ERR_ARG, "linear: NULL");
+  // dense bf16 problems that fit the tensor-core kernel's rules go there
+  if (dtype == NVLLM_BF16 && batch == 1 && k % 64 == 0 && n % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0 &&
+      aligned16(y) && aligned16(x) && aligned16(w))
+    return nvllm_gemm_bf16(y, x, w, m, n, k, ldx, ldw, ldy, out_dtype, nullptr, 0, stream);
+  LinArgs a{y, x, w, m, n, k, ldx, ldw, ldy, bsx, bsw, bsy, nullptr, nullptr, 0, 0.f};
+  return launch_tile<false>(a, (m + BM - 1) / BM, batch, dtype, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvllm_linear_grouped(void* y, const void* x, const void* w, int32_t max_rows, int32_t n, int32_t k,
+                                    int64_t ldx, int64_t ldw, int64_t ldy, int64_t group_stride_w, const int32_t* row_src,
+                                    const int32_t* tile_group, int32_t glu, float limit, int32_t dtype, int32_t out_dtype,
+                                    void* stream) {
+  NVLLM_CHECK_ARG(max_rows >= 0 && n > 0 && k > 0 && max_rows % BM == 0, NVLLM_ERR_ARG,
+                  "linear_grouped: max_rows=%d (multiple of 32) n=%d k=%d", max_rows, n, k);
+  NVLLM_CHECK_ARG((dtype == NVLLM_BF16 || dtype == NVLLM_F32) && (out_dtype == NVLLM_BF16 || out_dtype == NVLLM_F32),
+                  NVLLM_ERR_DTYPE, "linear_grouped: dtype %d / %d", dtype, out_dtype);
+  if (max_rows == 0) return 0;
+  NVLLM_CHECK_ARG(y && x && w, NVLLM_ERR_ARG, "linear_grouped: NULL");
+  // GLU: every group's weight block is [gate rows (n) | up rows (n)] x k
+  LinArgs a{y, x, w, max_rows, n, k, ldx, ldw, ldy, 0, group_stride_w, 0, row_src, tile_group,
+            static_cast<int64_t>(n) * ldw, limit};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return glu ? launch_tile<true>(a, max_rows / BM, 1, dtype, out_dtype, st)
+             : launch_tile<false>(a, max_rows / BM, 1, dtype, out_dtype, st);
+}
+
+extern "C" int nvllm_glu_clamped(void* out, const void* gate_up, int32_t n, int32_t ff, float limit, int32_t dtype,
+                                 void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && ff > 0, NVLLM_ERR_ARG, "glu_clamped: n=%d ff=%d", n, ff);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(out && gate_up, NVLLM_ERR_ARG, "glu_clamped: NULL");
+  const int64_t total = static_cast<int64_t>(n) * ff;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == NVLLM_BF16)
+    glu_clamped_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(gate_up), n, ff, limit);
+  else if (dtype == NVLLM_F32)
+    glu_clamped_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), n, ff, limit);
+  else NVLLM_CHECK_ARG(false, NVLLM_ERR_DTYPE, "glu_clamped: dtype %d", dtype);
+  NVLLM_LAUNCH_CHECK("glu_clamped_kernel");
+  return 0;
+}

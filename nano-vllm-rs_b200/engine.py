@@ -33,11 +33,11 @@ class CSamplingParams(C.Structure):
 class CBatch(C.Structure):
     """nvllm_batch."""
     _fields_ = [("is_prefill", i32), ("num_seqs", i32), ("num_tokens", i32), ("max_seqlen_q", i32),
-                ("max_seqlen_k", i32), ("max_blocks", i32), ("has_block_tables", i32), ("reserved", i32),
+                ("max_seqlen_k", i32), ("max_blocks", i32), ("has_block_tables", i32), ("num_logit_rows", i32),
                 ("seq_ids", C.POINTER(i64)), ("input_ids", C.POINTER(i64)), ("positions", C.POINTER(i64)),
                 ("slot_mapping", C.POINTER(i32)), ("cu_seqlens_q", C.POINTER(i32)), ("cu_seqlens_k", C.POINTER(i32)),
                 ("context_lens", C.POINTER(i32)), ("block_tables", C.POINTER(i32)), ("temperatures", C.POINTER(f32)),
-                ("top_k", C.POINTER(i32)), ("top_p", C.POINTER(f32))]
+                ("top_k", C.POINTER(i32)), ("top_p", C.POINTER(f32)), ("logit_rows", C.POINTER(i32))]
 
 
 class CSchedStats(C.Structure):
@@ -62,7 +62,17 @@ ENGINE_PROTOTYPES = {
     "nvllm_scheduler_free_list": (i32, [vp, vp, i32]),
     "nvllm_scheduler_sequence": (i32, [vp, i64, vp, i32, C.POINTER(i32), C.POINTER(i32)]),
     "nvllm_scheduler_release_sequence": (i32, [vp, i64]),
+    "nvllm_scheduler_extend_sequence": (i32, [vp, i64, vp, i32]),
+    "nvllm_scheduler_schedule_chunks": (i32, [vp, vp, vp, i32, C.POINTER(CBatch)]),
+    "nvllm_scheduler_commit_chunks": (i32, [vp]),
+    "nvllm_scheduler_finish_sequence": (i32, [vp, i64]),
+    "nvllm_registered_architectures": (C.c_char_p, []),
+    "nvllm_config_init_for_model": (i32, [C.POINTER(CConfig), C.c_char_p]),
     "nvllm_runner_create": (i32, [C.POINTER(vp), C.POINTER(CConfig), vp]),
+    "nvllm_runner_create_for_model": (i32, [C.POINTER(vp), C.POINTER(CConfig), C.c_char_p, i32, vp]),
+    "nvllm_runner_layer_tap": (i32, [vp, vp]),
+    "nvllm_engine_create_for_model": (i32, [C.POINTER(vp), C.POINTER(CConfig), C.c_char_p, i32, vp]),
+    "nvllm_engine_step_chunks": (i32, [vp, vp, vp, i32, vp, i32, vp]),
     "nvllm_runner_destroy": (i32, [vp]),
     "nvllm_runner_init_weights": (i32, [vp, u64, f32]),
     "nvllm_runner_load_weight": (i32, [vp, C.c_char_p, vp, i64, i64]),
@@ -103,6 +113,9 @@ def lib():
 # ---------------------------------------------------------------------------- Config / SamplingParams
 
 
+DTYPES = {"bfloat16": 0, "float32": 1}   # nvllm_dtype
+
+
 @dataclass
 class SamplingParams:
     """sampling_params.rs:10-88."""
@@ -125,12 +138,53 @@ class Config:
     """config.rs:16-186 + Qwen3Config (qwen3.rs:26-125).  `arch` picks a named architecture's dimensions;
     any field can be overridden by keyword (same names as the reference's fields)."""
 
-    def __init__(self, arch="qwen3-0.6b", **overrides):
+    def __init__(self, arch="qwen3-0.6b", model_config=None, dtype="bfloat16", **overrides):
+        """`arch`: a built-in named architecture.  `model_config`: the text (or dict) of a config.json whose `architecture`
+        key names a registered model (the registry lives in libnvllm.so: nvllm_registered_architectures); `dtype`
+        ("bfloat16" | "float32") is how such a model is run."""
         self.c = CConfig()
-        check(lib().nvllm_config_init(C.byref(self.c), arch.encode()))
+        self.model_json = None
+        self.dtype = dtype
+        if dtype not in DTYPES:
+            raise ValueError(f"dtype {dtype!r}: one of {sorted(DTYPES)}")
+        if model_config is not None:
+            import json as _json
+            self.model_json = model_config if isinstance(model_config, str) else _json.dumps(model_config)
+            check(lib().nvllm_config_init_for_model(C.byref(self.c), self.model_json.encode()))
+            arch = _json.loads(self.model_json).get("architecture", "")
+        else:
+            if dtype != "bfloat16":
+                raise ValueError("the built-in Qwen3 architectures run in bfloat16 only")
+            check(lib().nvllm_config_init(C.byref(self.c), arch.encode()))
         self.arch = arch
         for k, v in overrides.items():
             self._set(k, v)
+
+    @staticmethod
+    def from_pretrained(model_dir, dtype="bfloat16", **overrides):
+        """Reads <model_dir>/config.json and picks the model class by it: a Hugging Face Qwen3 configuration
+        ("architectures": ["Qwen3ForCausalLM"], its field names) fills the built-in Qwen3 fields; a configuration with an
+        `architecture` key goes to the model registry."""
+        import json as _json
+        import os as _os
+        with open(_os.path.join(model_dir, "config.json")) as f:
+            text = f.read()
+        d = _json.loads(text)
+        if "architecture" in d:
+            return Config(model_config=text, dtype=dtype, **overrides)
+        archs = d.get("architectures") or []
+        if not any("Qwen3" in a for a in archs):
+            raise ValueError(f"{model_dir}/config.json: no registered model for {archs or d.get('model_type')!r} "
+                             f"(known: {lib().nvllm_registered_architectures().decode()})")
+        cfg = Config("qwen3-0.6b", dtype=dtype)
+        for k in ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+                  "num_key_value_heads", "head_dim", "max_position_embeddings", "rms_norm_eps", "rope_theta"):
+            if k in d:
+                cfg._set(k, d[k])
+        cfg._set("tie_word_embeddings", int(bool(d.get("tie_word_embeddings", False))))
+        for k, v in overrides.items():
+            cfg._set(k, v)
+        return cfg
 
     def _set(self, k, v):
         if k == "eos_token_id":
@@ -142,7 +196,7 @@ class Config:
         setattr(self.c, k, int(v) if not isinstance(v, float) else v)
 
     def __getattr__(self, k):
-        if k in ("c", "arch"):
+        if k in ("c", "arch", "model_json", "dtype"):
             raise AttributeError(k)
         return getattr(self.c, k)
 
@@ -154,7 +208,8 @@ class Config:
     def with_enforce_eager(self, v): self._set("enforce_eager", v); return self
 
     def validate(self):
-        check(lib().nvllm_config_validate(C.byref(self.c)))
+        if self.model_json is None:   # a registered model checks its own configuration when the runner is created
+            check(lib().nvllm_config_validate(C.byref(self.c)))
         return self
 
 
@@ -246,6 +301,24 @@ class Scheduler:
         lib().nvllm_scheduler_free_list(self.h, a.ctypes.data, n)
         return a[:n].tolist()
 
+    # ---- explicit stepping (nvllm_engine.h): the caller names the sequences of a step and their token counts ----
+    def extend_sequence(self, seq_id, token_ids):
+        a = np.ascontiguousarray(token_ids, dtype=np.int64)
+        check(lib().nvllm_scheduler_extend_sequence(self.h, seq_id, a.ctypes.data, a.size))
+
+    def schedule_chunks(self, seq_ids, counts) -> Batch:
+        ids = np.ascontiguousarray(seq_ids, dtype=np.int64)
+        cnt = np.ascontiguousarray(counts, dtype=np.int32)
+        cb = CBatch()
+        check(lib().nvllm_scheduler_schedule_chunks(self.h, ids.ctypes.data, cnt.ctypes.data, ids.size, C.byref(cb)))
+        return Batch(cb)
+
+    def commit_chunks(self):
+        check(lib().nvllm_scheduler_commit_chunks(self.h))
+
+    def finish_sequence(self, seq_id):
+        check(lib().nvllm_scheduler_finish_sequence(self.h, seq_id))
+
     def release_sequence(self, seq_id):
         """Frees a FINISHED sequence's storage (its outputs have been handed to the caller); sequence(seq_id) raises
         KeyError afterwards."""
@@ -273,10 +346,15 @@ class ModelRunner:
         self._owned = _handle is None
         if _handle is None:
             h = vp()
-            check(lib().nvllm_runner_create(C.byref(h), C.byref(config.c), comm))
+            if config.model_json is not None:
+                check(lib().nvllm_runner_create_for_model(C.byref(h), C.byref(config.c), config.model_json.encode(),
+                                                          DTYPES[config.dtype], comm))
+            else:
+                check(lib().nvllm_runner_create(C.byref(h), C.byref(config.c), comm))
             _handle = h
         self.h = _handle
         self.vshard = config.vocab_size // config.tensor_parallel_size
+        self._tap = None
 
     def __del__(self):
         if getattr(self, "_owned", False) and self.h:
@@ -292,13 +370,34 @@ class ModelRunner:
         rows, cols = (1, a.shape[0]) if a.ndim == 1 else a.shape
         check(lib().nvllm_runner_load_weight(self.h, name.encode(), a.ctypes.data, rows, cols))
 
-    def execute_model(self, batch: Batch, return_logits=False):
-        """execute_model + sample_tokens (model_runner.rs:105-156): returns the sampled token ids [num_seqs] (and logits)."""
+    def layer_tap(self, max_tokens=None):
+        """Registered architectures, eager steps: after the next execute, `tap()[:runs, :tokens]` holds the f32 residual
+        stream after every layer run.  layer_tap(None) switches it off."""
+        if max_tokens is None:
+            check(lib().nvllm_runner_layer_tap(self.h, None))
+            self._tap = None
+            return None
+        self._tap = np.zeros((self.config.num_hidden_layers, max_tokens, self.config.hidden_size), np.float32)
+        check(lib().nvllm_runner_layer_tap(self.h, self._tap.ctypes.data))
+        return self._tap
+
+    def execute_model(self, batch: Batch, return_logits=False, logit_rows=None):
+        """execute_model + sample_tokens (model_runner.rs:105-156): returns the sampled token ids [num_seqs] (and logits).
+        logit_rows (prefill-kind batches): indices of the batch's tokens whose logits are computed instead of the last
+        token of every sequence."""
         n = batch.c.num_seqs
         toks = np.zeros(n, np.int64)
-        logits = np.zeros((n, self.vshard), np.float32) if return_logits else None
+        rows = n
+        if logit_rows is not None:
+            self._rows = np.ascontiguousarray(logit_rows, dtype=np.int32)
+            keep = self._rows if self._rows.size else np.zeros(1, np.int32)
+            batch.c.logit_rows = keep.ctypes.data_as(C.POINTER(i32))
+            batch.c.num_logit_rows = self._rows.size
+            self._rows_keep = keep
+            rows = self._rows.size
+        logits = np.zeros((rows, self.vshard), np.float32) if return_logits else None
         check(lib().nvllm_runner_execute(self.h, C.byref(batch.c), toks.ctypes.data,
-                                         logits.ctypes.data if return_logits else None))
+                                         logits.ctypes.data if (return_logits and rows) else None))
         return (toks, logits) if return_logits else toks
 
     def profile(self, enable=True):
@@ -357,7 +456,11 @@ class LLMEngine:
         self.is_running = True
         self._live = {}     # seq_id -> tokens already reported (for step outputs / streaming)
         h = vp()
-        check(lib().nvllm_engine_create(C.byref(h), C.byref(config.c), comm))
+        if config.model_json is not None:
+            check(lib().nvllm_engine_create_for_model(C.byref(h), C.byref(config.c), config.model_json.encode(),
+                                                      DTYPES[config.dtype], comm))
+        else:
+            check(lib().nvllm_engine_create(C.byref(h), C.byref(config.c), comm))
         self.h = h
         self.scheduler = Scheduler(config, _handle=vp(lib().nvllm_engine_scheduler(h)))
         self.model_runner = ModelRunner(config, _handle=vp(lib().nvllm_engine_runner(h)))
@@ -396,6 +499,28 @@ class LLMEngine:
 
     def is_finished(self):
         return bool(lib().nvllm_engine_is_finished(self.h))
+
+    @staticmethod
+    def from_pretrained(model_dir, dtype="bfloat16", comm=None, tokenizer=None, **overrides):
+        """Engine for the checkpoint in model_dir: config.json picks the model class (Config.from_pretrained), every
+        *.safetensors file of the folder is loaded through the runner."""
+        from .loader import ModelLoader
+        eng = LLMEngine(Config.from_pretrained(model_dir, dtype=dtype, **overrides), comm=comm, init_weights=False,
+                        tokenizer=tokenizer)
+        ModelLoader(eng.model_runner).load_safetensors_dir(model_dir)
+        return eng
+
+    def step_chunks(self, seq_ids, counts, logit_rows=()):
+        """One explicit step (nvllm_engine_step_chunks): runs the next counts[i] tokens of sequence seq_ids[i] as one batch
+        and returns the f32 logits [len(logit_rows), vocab] of the named tokens of the step."""
+        ids = np.ascontiguousarray(seq_ids, dtype=np.int64)
+        cnt = np.ascontiguousarray(counts, dtype=np.int32)
+        rows = np.ascontiguousarray(logit_rows, dtype=np.int32)
+        out = np.zeros((rows.size, self.model_runner.vshard), np.float32)
+        check(lib().nvllm_engine_step_chunks(self.h, ids.ctypes.data, cnt.ctypes.data, ids.size,
+                                             rows.ctypes.data if rows.size else None, rows.size,
+                                             out.ctypes.data if rows.size else None))
+        return out
 
     def _output(self, sid, s):
         n = s["num_prompt_tokens"]

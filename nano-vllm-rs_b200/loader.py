@@ -83,9 +83,10 @@ class ModelLoader:
     def load_safetensors(self, path):
         n = 0
         for name, dtype, shape, raw in read_safetensors(path):
-            if len(shape) not in (1, 2):
+            if len(shape) not in (0, 1, 2):
                 raise ValueError(f"{name}: unsupported rank {len(shape)}")
-            self.runner.load_weight(name, to_bf16_bits(dtype, shape, raw))   # slices + packs on the device side
+            bits = to_bf16_bits(dtype, shape, raw)
+            self.runner.load_weight(name, bits.reshape(1) if bits.ndim == 0 else bits)   # slices + packs on the device side
             n += 1
         return n
 
