@@ -254,3 +254,102 @@ def init_weight(shape, seed, tensor_id, std, dtype=torch.bfloat16, device="cuda"
     t = torch.empty(shape, dtype=dtype, device=device)
     check(_ffi.lib().nvllm_init_weight(_p(t), t.numel(), seed, tensor_id, std, BF16 if dtype == torch.bfloat16 else F32, _stream()))
     return t
+
+
+# ---------------------------------------------------------------------------- mechanisms of registered architectures
+# (latent attention, Dynamic Tanh norms, mixture of experts: include/nvllm.h, last section).  Operands are bf16 or f32.
+
+
+def _dt(t):
+    if t.dtype == torch.bfloat16:
+        return BF16
+    if t.dtype == torch.float32:
+        return F32
+    raise ValueError(f"expected bfloat16 or float32, got {t.dtype}")
+
+
+def linear(x, w, out_dtype=None, batch=1, bsx=0, bsw=0, bsy=0, out=None, n=None, k=None):
+    """y = x . w^T (nvllm_linear).  x [m, ldx], w [n, ldw] (views with a row stride are fine); batch > 1: element strides."""
+    m = x.shape[0]
+    n = w.shape[0] if n is None else n
+    k = w.shape[1] if k is None else k
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty((m, n * batch if bsy == n else n), dtype=out_dtype, device=x.device)
+    check(_ffi.lib().nvllm_linear(_p(out), _p(x), _p(w), m, n, k, x.stride(0), w.stride(0), out.stride(0), batch, bsx, bsw, bsy,
+                                  _dt(x), _dt(out), _stream()))
+    return out
+
+
+def linear_grouped(x, w, row_src, tile_group, max_rows, n, k, group_stride_w, glu=False, limit=0.0, ldw=None):
+    out = torch.zeros((max_rows, n), dtype=x.dtype, device=x.device)
+    check(_ffi.lib().nvllm_linear_grouped(_p(out), _p(x), _p(w), max_rows, n, k, x.stride(0), ldw or k, n, group_stride_w,
+                                          _p(row_src), _p(tile_group), int(glu), limit, _dt(x), _dt(x), _stream()))
+    return out
+
+
+def glu_clamped(gate_up, limit):
+    n, ff2 = gate_up.shape
+    out = torch.empty((n, ff2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    check(_ffi.lib().nvllm_glu_clamped(_p(out), _p(gate_up), n, ff2 // 2, limit, _dt(gate_up), _stream()))
+    return out
+
+
+def dyt_residual_norm(h, y=None, post=None, pre=None, dtype=torch.bfloat16):
+    """h (f32 [n, hidden], in place) += dyt_post(y); returns dyt_pre(h) (or None).  post / pre: (alpha[1], w, b) f32 tensors."""
+    n, hidden = h.shape
+    out = torch.empty((n, hidden), dtype=dtype, device=h.device) if pre is not None else None
+    pa, pw, pb = post if post is not None else (None, None, None)
+    qa, qw, qb = pre if pre is not None else (None, None, None)
+    check(_ffi.lib().nvllm_dyt_residual_norm(_p(out), _p(h), _p(y), _p(pa), _p(pw), _p(pb), _p(qa), _p(qw), _p(qb), n, hidden,
+                                             _dt(y) if y is not None else _dt(out), _stream()))
+    return out
+
+
+def rope_table_interleaved(max_pos, dims, base, device):
+    tab = torch.empty((max_pos, dims // 2, 2), dtype=torch.float32, device=device)
+    check(_ffi.lib().nvllm_rope_table_interleaved(_p(tab), max_pos, dims, float(base), _stream()))
+    return tab
+
+
+def latent_prepare(q, dkv, c_norm_w, eps, positions, table, rot_dims, heads, dim, rot_dim, kv_rank, cache, slots):
+    """In place on q; writes cache rows (cache: [slots, row] tensor)."""
+    check(_ffi.lib().nvllm_latent_prepare(_p(q), q.stride(0), _p(dkv), dkv.stride(0), _p(c_norm_w), eps, _p(positions), _p(table),
+                                          rot_dims, table.shape[0] if table is not None else 1, q.shape[0], heads, dim, rot_dim,
+                                          kv_rank, _p(cache), cache.stride(0), _p(slots), _dt(q), _stream()))
+
+
+def latent_attention(q_abs, q, tok_seq, positions, tables, block_size, cache, heads, dim, rot_dim, kv_rank, scale):
+    n = q.shape[0]
+    out = torch.empty((n, heads * kv_rank), dtype=q.dtype, device=q.device)
+    check(_ffi.lib().nvllm_latent_attention(_p(out), out.stride(0), _p(q_abs), q_abs.stride(0), _p(q), q.stride(0), _p(tok_seq),
+                                            _p(positions), _p(tables), tables.shape[1], block_size, _p(cache), cache.stride(0), n,
+                                            heads, dim, rot_dim, kv_rank, scale, _dt(q), _stream()))
+    return out
+
+
+def moe_route(logits, bias, top, scale):
+    n, e = logits.shape
+    idx = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    check(_ffi.lib().nvllm_moe_route(_p(idx), _p(w), _p(logits), _p(bias), n, e, top, scale, _stream()))
+    return idx, w
+
+
+def moe_sort(topk_idx, experts):
+    n, top = topk_idx.shape
+    rows = _ffi.lib().nvllm_moe_max_rows(n, top, experts)
+    dev = topk_idx.device
+    row_token = torch.empty(rows, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(rows // 32, dtype=torch.int32, device=dev)
+    slot_row = torch.empty((n, top), dtype=torch.int32, device=dev)
+    check(_ffi.lib().nvllm_moe_sort(_p(row_token), _p(tile_expert), _p(slot_row), _p(topk_idx), n, top, experts, rows, _stream()))
+    return row_token, tile_expert, slot_row
+
+
+def moe_combine(expert_out, x, shared_out, topk_idx, topk_w, slot_row, experts):
+    n, hidden = x.shape
+    out = torch.empty_like(x)
+    check(_ffi.lib().nvllm_moe_combine(_p(out), _p(expert_out), _p(x), _p(shared_out), _p(topk_idx), _p(topk_w), _p(slot_row), n,
+                                       hidden, topk_idx.shape[1], experts, _dt(x), _stream()))
+    return out
