@@ -398,13 +398,18 @@ int nvllm_latent_attention(void* out, int64_t ldo, const float* q_abs, int64_t l
  *   topk_w[k] = s[chosen_k] / (sum_k s[chosen_k] + 1e-20) * scale.   outputs <= 1536. */
 int nvllm_moe_route(int32_t* topk_idx, float* topk_w, const float* logits, const float* bias, int32_t n, int32_t outputs,
                     int32_t top, float scale, void* stream);
-/* Rows the grouped buffers need for n tokens (every expert's segment starts on a 32-row tile). */
-int32_t nvllm_moe_max_rows(int32_t n_tokens, int32_t top, int32_t experts);
-/* Counting sort of the (token, slot) assignments by expert for nvllm_linear_grouped: row_token[max_rows] (token of each
- * row, -1 padding), tile_expert[max_rows / 32] (-1 unused), slot_row[n * top] (row of each assignment; -1 when it chose an
- * identity expert, i.e. an index >= experts). */
+/* Rows the grouped buffers need for n tokens when every expert's segment starts on a tile of tile_rows rows. */
+int32_t nvllm_moe_max_rows(int32_t n_tokens, int32_t top, int32_t experts, int32_t tile_rows);
+/* Counting sort of the (token, slot) assignments by expert for the grouped products (tile_rows 32: nvllm_linear_grouped,
+ * 128: nvllm_gemm_bf16_grouped): row_token[max_rows] (token of each row, -1 padding), tile_expert[max_rows / tile_rows]
+ * (-1 unused), slot_row[n * top] (row of each assignment; -1 when it chose an identity expert, i.e. an index >= experts). */
 int nvllm_moe_sort(int32_t* row_token, int32_t* tile_expert, int32_t* slot_row, const int32_t* topk_idx, int32_t n,
-                   int32_t top, int32_t experts, int32_t max_rows, void* stream);
+                   int32_t top, int32_t experts, int32_t max_rows, int32_t tile_rows, void* stream);
+/* Tensor-core grouped product (bf16): rows in 128-row tiles, tile i times the weight block of group tile_group[i], i.e.
+ * rows [group * n, (group + 1) * n) of w ([groups * n, k]); an unused tile (group < 0) is computed against group 0 and its
+ * rows mean nothing.  k % 64 == 0, n % 8 == 0, 16-byte aligned rows. */
+int nvllm_gemm_bf16_grouped(void* y, const void* x, const void* w, int32_t max_rows, int32_t n, int32_t k, int32_t groups,
+                            int64_t ldx, int64_t ldw, int64_t ldy, const int32_t* tile_group, void* stream);
 /* out[t] = sum_k topk_w[t, k] * (slot_row[t, k] >= 0 ? expert_out[slot_row[t, k]] : x[t]) + shared_out[t] (nullable). */
 int nvllm_moe_combine(void* out, const void* expert_out, const void* x, const void* shared_out, const int32_t* topk_idx,
                       const float* topk_w, const int32_t* slot_row, int32_t n, int32_t hidden, int32_t top, int32_t experts,

@@ -87,8 +87,9 @@ PROTOTYPES = {
     "nvllm_latent_prepare": (i32, [vp, i64, vp, i64, vp, f32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp, i64, vp, i32, vp]),
     "nvllm_latent_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, vp, i32, i32, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp]),
     "nvllm_moe_route": (i32, [vp, vp, vp, vp, i32, i32, i32, f32, vp]),
-    "nvllm_moe_max_rows": (i32, [i32, i32, i32]),
-    "nvllm_moe_sort": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "nvllm_moe_max_rows": (i32, [i32, i32, i32, i32]),
+    "nvllm_moe_sort": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "nvllm_gemm_bf16_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, i64, i64, i64, vp, vp]),
     "nvllm_moe_combine": (i32, [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
 }
 

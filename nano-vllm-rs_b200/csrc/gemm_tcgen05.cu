@@ -100,7 +100,10 @@ template <int BN, typename OutT, bool SILU, int CN, bool ROPE = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
                     OutT* __restrict__ y, int M, int N, int K, int64_t ldy, int num_m_tiles, int num_tiles,
-                    const RopeEpi re = RopeEpi{}, int STAGES = GemmCfg<BN>::kStages, const RowPush ps = RowPush{}) {
+                    const RopeEpi re = RopeEpi{}, int STAGES = GemmCfg<BN>::kStages, const RowPush ps = RowPush{},
+                    const int32_t* __restrict__ tile_group = nullptr, int group_rows = 0) {
+  // tile_group != nullptr (expert layers): 128-row tile m uses the weight block of group tile_group[m], i.e. rows
+  // [group * group_rows, ...) of w; an unused tile (group < 0) runs against group 0 and its rows are never read.
   using C = GemmCfg<BN>;  // STAGES <= C::kStages: ring depth of this launch (fewer stages -> two CTAs per SM, see launch_gemm)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // SWIZZLE_128B tiles: 1024-byte aligned
@@ -148,12 +151,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // ===== TMA producer =====
     // The weights do not depend on the previous kernel: the first ring of w tiles is requested BEFORE the
     // programmatic-dependency wait, so their HBM latency hides behind the predecessor's tail; x follows after it.
-    auto load_w = [&](int stage, int kb, int n_tile) {
+    auto load_w = [&](int stage, int kb, int n_tile, int goff = 0) {
       if constexpr (SILU) {
-        tma_load_2d(sB + stage * C::kBBytes, &tmap_w, full_bar(stage), kb * C::BK, n_tile * (BN / 2));
-        tma_load_2d(sB + stage * C::kBBytes + (BN / 2) * 128, &tmap_w, full_bar(stage), kb * C::BK, N + n_tile * (BN / 2));
+        tma_load_2d(sB + stage * C::kBBytes, &tmap_w, full_bar(stage), kb * C::BK, goff + n_tile * (BN / 2));
+        tma_load_2d(sB + stage * C::kBBytes + (BN / 2) * 128, &tmap_w, full_bar(stage), kb * C::BK, goff + N + n_tile * (BN / 2));
       } else {
-        tma_load_2d(sB + stage * C::kBBytes, &tmap_w, full_bar(stage), kb * C::BK, n_tile * BN);
+        tma_load_2d(sB + stage * C::kBBytes, &tmap_w, full_bar(stage), kb * C::BK, goff + n_tile * BN);
       }
     };
     auto load_x = [&](int stage, int kb, int m_tile) {
@@ -165,7 +168,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
         tma_load_2d(sA + stage * C::kABytes, &tmap_x, full_bar(stage), kb * C::BK, m_tile * C::BM);
       }
     };
-    const int pre = num_kb < STAGES ? num_kb : STAGES;
+    // (grouped launches read the tile's group, which the previous kernel wrote: no weight tile before the wait)
+    const int pre = tile_group != nullptr ? 0 : (num_kb < STAGES ? num_kb : STAGES);
     {
       const int n_tile0 = (cta0 / num_m_tiles) * CN + rank;
       for (int kb = 0; kb < pre; ++kb) {
@@ -179,6 +183,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     bool first = true;
     for (int tile = cta0; tile < num_tiles; tile += cta_stride) {
       const int m_tile = tile % num_m_tiles, n_tile = (tile / num_m_tiles) * CN + rank;
+      int goff = 0;
+      if (tile_group != nullptr) { const int g = tile_group[m_tile]; goff = (g > 0 ? g : 0) * group_rows; }
       for (int kb = 0; kb < num_kb; ++kb) {
         if (first && kb < pre) {  // w tile already in flight, barrier already armed
           load_x(stage, kb, m_tile);
@@ -186,7 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
           mbar_wait(empty_bar(stage), phase ^ 1);
           mbar_expect_tx(full_bar(stage), C::kStageBytes);
           load_x(stage, kb, m_tile);
-          load_w(stage, kb, n_tile);
+          load_w(stage, kb, n_tile, goff);
         }
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
@@ -344,7 +350,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 
 template <int BN, typename OutT, bool SILU = false, int CN = 1, bool ROPE = false>
 static int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, void* y, int M, int N, int K, int64_t ldy,
-                       cudaStream_t st, const RopeEpi& re = RopeEpi{}, const RowPush& ps = RowPush{}) {
+                       cudaStream_t st, const RopeEpi& re = RopeEpi{}, const RowPush& ps = RowPush{},
+                       const int32_t* tile_group = nullptr, int group_rows = 0) {
   using C = GemmCfg<BN>;
   auto kern = gemm_tcgen05_kernel<BN, OutT, SILU, CN, ROPE>;
   NVLLM_SMEM_ATTR_ONCE(kern, C::kSmemBytes);
@@ -364,7 +371,7 @@ static int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, void* y, in
   const int smem = C::kSmemBytes - (C::kStages - stages) * C::kStageBytes;
   if constexpr (CN == 1) {
     NVLLM_CUDA(launch_pdl(kern, dim3(clusters), dim3(256), smem, st, tx, tw, static_cast<OutT*>(y), M, N, K, ldy,
-                          num_m_tiles, num_tiles, re, stages, ps));
+                          num_m_tiles, num_tiles, re, stages, ps, tile_group, group_rows));
   } else {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(clusters * CN);
@@ -379,7 +386,7 @@ static int launch_gemm(const CUtensorMap& tx, const CUtensorMap& tw, void* y, in
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     NVLLM_CUDA(cudaLaunchKernelEx(&cfg, kern, tx, tw, static_cast<OutT*>(y), M, N, K, ldy, num_m_tiles, num_tiles, re,
-                                  static_cast<int>(C::kStages), ps));
+                                  static_cast<int>(C::kStages), ps, tile_group, group_rows));
   }
   return 0;
 }
@@ -506,6 +513,31 @@ extern "C" int nvllm_gemm_bf16(void* y, const void* x, const void* w, int32_t m,
                                size_t workspace_bytes, void* stream) {
   (void)workspace; (void)workspace_bytes;
   return nvllm::gemm_bf16_impl(y, x, w, m, n, k, ldx, ldw, ldy, out_dtype, stream, nvllm::RowPush{});
+}
+
+// Grouped GEMM for expert layers: rows come in 128-row tiles, tile i multiplies with the weight block of group
+// tile_group[i] (rows [group * n, (group + 1) * n) of w).  Same kernel as nvllm_gemm_bf16, single-CTA tiles.
+extern "C" int nvllm_gemm_bf16_grouped(void* y, const void* x, const void* w, int32_t max_rows, int32_t n, int32_t k,
+                                       int32_t groups, int64_t ldx, int64_t ldw, int64_t ldy, const int32_t* tile_group,
+                                       void* stream) {
+  using namespace nvllm;
+  NVLLM_CHECK_ARG(max_rows >= 0 && max_rows % 128 == 0 && n > 0 && k > 0 && groups > 0 && k % 64 == 0 && n % 8 == 0, NVLLM_ERR_ARG,
+                  "gemm_grouped: max_rows=%d (multiple of 128) n=%d (%% 8) k=%d (%% 64) groups=%d", max_rows, n, k, groups);
+  NVLLM_CHECK_ARG(ldx >= k && ldw >= k && ldy >= n && ldx % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0, NVLLM_ERR_ALIGN,
+                  "gemm_grouped: leading dimensions");
+  if (max_rows == 0) return 0;
+  NVLLM_CHECK_ARG(y && x && w && tile_group && aligned16(y) && aligned16(x) && aligned16(w), NVLLM_ERR_ALIGN, "gemm_grouped: pointers");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int bn = n >= 256 ? 256 : (n >= 128 ? 128 : (n >= 64 ? 64 : 32));
+  CUtensorMap tx, tw;
+  if (int rc = make_tmap_bf16_2d(&tx, x, max_rows, k, ldx, 128)) return rc;
+  if (int rc = make_tmap_bf16_2d(&tw, w, static_cast<int64_t>(groups) * n, k, ldw, bn)) return rc;
+  switch (bn) {
+    case 256: return launch_gemm<256, bf16>(tx, tw, y, max_rows, n, k, ldy, st, RopeEpi{}, RowPush{}, tile_group, n);
+    case 128: return launch_gemm<128, bf16>(tx, tw, y, max_rows, n, k, ldy, st, RopeEpi{}, RowPush{}, tile_group, n);
+    case 64: return launch_gemm<64, bf16>(tx, tw, y, max_rows, n, k, ldy, st, RopeEpi{}, RowPush{}, tile_group, n);
+    default: return launch_gemm<32, bf16>(tx, tw, y, max_rows, n, k, ldy, st, RopeEpi{}, RowPush{}, tile_group, n);
+  }
 }
 
 // MergedColumnParallelLinear::forward + SiluAndMul::forward in one call (linear.rs:437-439 + activation.rs:46-63).

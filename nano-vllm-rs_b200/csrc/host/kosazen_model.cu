@@ -12,6 +12,7 @@
 // expert.{ff,limit}, router.{experts,identity,top,scale}, shared.{ff,limit}).
 // tensors: embed, head, final.norm{,.alpha,.b}, l<i>.norm{1,1b,2,2b}{,.alpha,.b}, l<i>.mix.{q,dkv,dkv.norm,uk,uv,o},
 // l<i>.mlp.{router,correction,e<j>.{gate,up,down},shared.{gate,up,down}}.
+#include <algorithm>
 #include <cmath>
 #include <map>
 #include <set>
@@ -48,6 +49,7 @@ struct Layer {
   void *router = nullptr, *egu = nullptr, *edown = nullptr, *sgu = nullptr, *sdown = nullptr;
   float* correction = nullptr;
   const float* rope = nullptr;
+  int tile_rows = 32;  // 128: experts run on the tensor-core grouped GEMM (bf16, aligned sizes), else the tile kernel
   int qdim() const { return heads * (dim + rot_dim); }
   int qd_n() const { return qdim() + kv_rank + rot_dim; }
   int cache_row() const { return (kv_rank + rot_dim + 7) / 8 * 8; }
@@ -69,7 +71,7 @@ class Kosazen : public ModelImpl {
   // activations
   float *h_ = nullptr, *q_abs_ = nullptr, *router_logits_ = nullptr, *topk_w_ = nullptr;
   void *normed_ = nullptr, *qd_ = nullptr, *o_lat_ = nullptr, *attn_ = nullptr, *proj_ = nullptr, *act_ = nullptr,
-       *eout_ = nullptr, *sgu_buf_ = nullptr, *sact_ = nullptr, *sout_ = nullptr, *moe_out_ = nullptr, *head_in_ = nullptr;
+       *eout_ = nullptr, *xg_ = nullptr, *egu_buf_ = nullptr, *sgu_buf_ = nullptr, *sact_ = nullptr, *sout_ = nullptr, *moe_out_ = nullptr, *head_in_ = nullptr;
   int32_t *topk_idx_ = nullptr, *row_token_ = nullptr, *tile_expert_ = nullptr, *slot_row_ = nullptr;
   int max_rows_ = 0, head_rows_ = 0;
   std::vector<void*> allocs_;
@@ -193,7 +195,8 @@ class Kosazen : public ModelImpl {
         }
         m_et = std::max(m_et, et); m_ff = std::max<size_t>(m_ff, L.ff); m_sff = std::max<size_t>(m_sff, L.sff);
         m_top = std::max<size_t>(m_top, L.top);
-        max_rows_ = std::max(max_rows_, nvllm_moe_max_rows(lim.max_tokens, L.top, L.experts));
+        if (dt_ == NVLLM_BF16 && L.experts > 0 && W % 64 == 0 && L.ff % 64 == 0) L.tile_rows = 128;
+        max_rows_ = std::max(max_rows_, nvllm_moe_max_rows(lim.max_tokens, L.top, L.experts, L.tile_rows));
       }
       m_qd = std::max<size_t>(m_qd, L.qd_n()); m_hr = std::max<size_t>(m_hr, static_cast<size_t>(L.heads) * L.kv_rank);
       m_hv = std::max<size_t>(m_hv, static_cast<size_t>(L.heads) * L.vdim);
@@ -225,6 +228,7 @@ class Kosazen : public ModelImpl {
       RUN(dalloc(&slot_row_, T * m_top)); RUN(dalloc(&row_token_, static_cast<size_t>(max_rows_) + 32));
       RUN(dalloc(&tile_expert_, static_cast<size_t>(max_rows_) / 32 + 1));
       RUN(oalloc(&act_, static_cast<size_t>(max_rows_) * (m_ff ? m_ff : 1))); RUN(oalloc(&eout_, static_cast<size_t>(max_rows_) * W));
+      RUN(oalloc(&xg_, static_cast<size_t>(max_rows_) * W)); RUN(oalloc(&egu_buf_, static_cast<size_t>(max_rows_) * 2 * (m_ff ? m_ff : 1)));
       RUN(oalloc(&sgu_buf_, T * 2 * (m_sff ? m_sff : 1))); RUN(oalloc(&sact_, T * (m_sff ? m_sff : 1))); RUN(oalloc(&sout_, T * W));
       RUN(oalloc(&moe_out_, T * W));
     }
@@ -387,14 +391,17 @@ class Kosazen : public ModelImpl {
     void* st = v.stream;
     const int N = v.n_tokens, W = width_;
     launches = 0;
-    auto lin = [&](void* y, const void* x, const void* w, int n, int k, int64_t ldx, int64_t ldy, int out_dt) {
+    auto mk = [&](const char* name) { if (v.mark) v.mark(v.mark_ctx, name); };
+    auto lin = [&](void* y, const void* x, const void* w, int n, int k, int64_t ldx, int64_t ldy, int out_dt, const char* name) {
       ++launches;
-      return nvllm_linear(y, x, w, N, n, k, ldx, k, ldy, 1, 0, 0, 0, dt_, out_dt, st);
+      const int rc = nvllm_linear(y, x, w, N, n, k, ldx, k, ldy, 1, 0, 0, 0, dt_, out_dt, st);
+      mk(name);
+      return rc;
     };
     const int act_dt = dt_;  // activations follow the model dtype
-    RUN(nvllm_embedding_gather_f32(h_, embed_, v.ids, N, W, vocab_, dt_, st)); ++launches;
+    RUN(nvllm_embedding_gather_f32(h_, embed_, v.ids, N, W, vocab_, dt_, st)); ++launches; mk("embedding_gather_f32");
     const Layer& first = layers_[runs_[0]];
-    RUN(nvllm_dyt_residual_norm(normed_, h_, nullptr, nullptr, nullptr, nullptr, first.n1.alpha, first.n1.w, first.n1.b, N, W, dt_, st)); ++launches;
+    RUN(nvllm_dyt_residual_norm(normed_, h_, nullptr, nullptr, nullptr, nullptr, first.n1.alpha, first.n1.w, first.n1.b, N, W, dt_, st)); ++launches; mk("dyt_residual_norm");
     for (size_t r = 0; r < runs_.size(); ++r) {
       const Layer& L = layers_[runs_[r]];
       const Dyt& next = r + 1 < runs_.size() ? layers_[runs_[r + 1]].n1 : final_;
@@ -402,46 +409,52 @@ class Kosazen : public ModelImpl {
       const int qh = L.dim + L.rot_dim;
       uint8_t* qd = static_cast<uint8_t*>(qd_);
       // q and the compressed kv in one projection: rows [q heads | latent | shared rotated key]
-      RUN(lin(qd_, normed_, L.qdkv, L.qd_n(), W, W, ldqd, act_dt));
+      RUN(lin(qd_, normed_, L.qdkv, L.qd_n(), W, W, ldqd, act_dt, "q + compressed kv projection"));
       RUN(nvllm_latent_prepare(qd_, ldqd, qd + static_cast<size_t>(L.qdim()) * esz_, ldqd, L.c_norm, eps_, v.positions, L.rope,
                                L.rot_dims, lim_.max_positions, N, L.heads, L.dim, L.rot_dim, L.kv_rank, cache_[r], L.cache_row(),
-                               v.slots, dt_, st)); ++launches;
+                               v.slots, dt_, st)); ++launches; mk("latent_prepare");
       // fold the key up-projection into the query: qa[t, h, :] = Uk_h^T q[t, h, :dim]  (f32)
       if (L.dim > 0) {
         RUN(nvllm_linear(q_abs_, qd_, L.ukT, N, L.kv_rank, L.dim, ldqd, L.dim, HR, L.heads, qh, static_cast<int64_t>(L.kv_rank) * L.dim,
-                         L.kv_rank, dt_, NVLLM_F32, st)); ++launches;
+                         L.kv_rank, dt_, NVLLM_F32, st)); ++launches; mk("q absorb (per-head linear)");
       } else {
         NVLLM_CUDA(cudaMemsetAsync(q_abs_, 0, static_cast<size_t>(N) * HR * 4, static_cast<cudaStream_t>(st)));
       }
       RUN(nvllm_latent_attention(o_lat_, HR, q_abs_, HR, qd_, ldqd, v.tok_seq, v.positions, v.tables, v.table_cap, lim_.block_size,
-                                 cache_[r], L.cache_row(), N, L.heads, L.dim, L.rot_dim, L.kv_rank, L.scale, dt_, st)); ++launches;
+                                 cache_[r], L.cache_row(), N, L.heads, L.dim, L.rot_dim, L.kv_rank, L.scale, dt_, st)); ++launches; mk("latent_attention");
       // values: per head Uv_h applied to the attended latent, then the output projection
       RUN(nvllm_linear(attn_, o_lat_, L.uv, N, L.vdim, L.kv_rank, HR, L.kv_rank, HV, L.heads, L.kv_rank,
-                       static_cast<int64_t>(L.vdim) * L.kv_rank, L.vdim, dt_, act_dt, st)); ++launches;
-      RUN(lin(proj_, attn_, L.o, W, static_cast<int>(HV), HV, W, act_dt));
+                       static_cast<int64_t>(L.vdim) * L.kv_rank, L.vdim, dt_, act_dt, st)); ++launches; mk("value up-projection (per-head linear)");
+      RUN(lin(proj_, attn_, L.o, W, static_cast<int>(HV), HV, W, act_dt, "attention output projection"));
       if (!L.has_mlp) {
-        RUN(nvllm_dyt_residual_norm(normed_, h_, proj_, L.n1b.alpha, L.n1b.w, L.n1b.b, next.alpha, next.w, next.b, N, W, dt_, st)); ++launches;
+        RUN(nvllm_dyt_residual_norm(normed_, h_, proj_, L.n1b.alpha, L.n1b.w, L.n1b.b, next.alpha, next.w, next.b, N, W, dt_, st)); ++launches; mk("dyt_residual_norm");
       } else {
-        RUN(nvllm_dyt_residual_norm(normed_, h_, proj_, L.n1b.alpha, L.n1b.w, L.n1b.b, L.n2.alpha, L.n2.w, L.n2.b, N, W, dt_, st)); ++launches;
+        RUN(nvllm_dyt_residual_norm(normed_, h_, proj_, L.n1b.alpha, L.n1b.w, L.n1b.b, L.n2.alpha, L.n2.w, L.n2.b, N, W, dt_, st)); ++launches; mk("dyt_residual_norm");
         const int et = L.experts + L.identity;
-        RUN(lin(router_logits_, normed_, L.router, et, W, W, et, NVLLM_F32));
-        RUN(nvllm_moe_route(topk_idx_, topk_w_, router_logits_, L.correction, N, et, L.top, L.router_scale, st)); ++launches;
-        const int rows = nvllm_moe_max_rows(N, L.top, L.experts);
-        RUN(nvllm_moe_sort(row_token_, tile_expert_, slot_row_, topk_idx_, N, L.top, L.experts, rows, st)); ++launches;
-        if (L.experts > 0) {
+        RUN(lin(router_logits_, normed_, L.router, et, W, W, et, NVLLM_F32, "router logits"));
+        RUN(nvllm_moe_route(topk_idx_, topk_w_, router_logits_, L.correction, N, et, L.top, L.router_scale, st)); ++launches; mk("moe_route");
+        const int rows = nvllm_moe_max_rows(N, L.top, L.experts, L.tile_rows);
+        RUN(nvllm_moe_sort(row_token_, tile_expert_, slot_row_, topk_idx_, N, L.top, L.experts, rows, L.tile_rows, st)); ++launches; mk("moe_sort");
+        if (L.experts > 0 && L.tile_rows == 128) {
+          // tensor cores: gather the rows by expert, [gate | up] in one grouped GEMM, activation, grouped down projection
+          RUN(nvllm_gather_rows(xg_, normed_, row_token_, rows, W, N, dt_, st)); ++launches; mk("expert row gather");
+          RUN(nvllm_gemm_bf16_grouped(egu_buf_, xg_, L.egu, rows, 2 * L.ff, W, L.experts, W, W, 2 * L.ff, tile_expert_, st)); ++launches; mk("expert gate_up grouped GEMM");
+          RUN(nvllm_glu_clamped(act_, egu_buf_, rows, L.ff, L.limit, dt_, st)); ++launches; mk("expert glu_clamped");
+          RUN(nvllm_gemm_bf16_grouped(eout_, act_, L.edown, rows, W, L.ff, L.experts, L.ff, L.ff, W, tile_expert_, st)); ++launches; mk("expert down grouped GEMM");
+        } else if (L.experts > 0) {
           RUN(nvllm_linear_grouped(act_, normed_, L.egu, rows, L.ff, W, W, W, L.ff, static_cast<int64_t>(2) * L.ff * W, row_token_,
-                                   tile_expert_, 1, L.limit, dt_, act_dt, st)); ++launches;
+                                   tile_expert_, 1, L.limit, dt_, act_dt, st)); ++launches; mk("expert gate_up+glu grouped tile kernel");
           RUN(nvllm_linear_grouped(eout_, act_, L.edown, rows, W, L.ff, L.ff, L.ff, W, static_cast<int64_t>(W) * L.ff, nullptr,
-                                   tile_expert_, 0, 0.f, dt_, act_dt, st)); ++launches;
+                                   tile_expert_, 0, 0.f, dt_, act_dt, st)); ++launches; mk("expert down grouped tile kernel");
         }
         if (L.has_shared) {
-          RUN(lin(sgu_buf_, normed_, L.sgu, 2 * L.sff, W, W, 2 * L.sff, act_dt));
-          RUN(nvllm_glu_clamped(sact_, sgu_buf_, N, L.sff, L.slimit, dt_, st)); ++launches;
-          RUN(lin(sout_, sact_, L.sdown, W, L.sff, L.sff, W, act_dt));
+          RUN(lin(sgu_buf_, normed_, L.sgu, 2 * L.sff, W, W, 2 * L.sff, act_dt, "shared gate_up projection"));
+          RUN(nvllm_glu_clamped(sact_, sgu_buf_, N, L.sff, L.slimit, dt_, st)); ++launches; mk("shared glu_clamped");
+          RUN(lin(sout_, sact_, L.sdown, W, L.sff, L.sff, W, act_dt, "shared down projection"));
         }
         RUN(nvllm_moe_combine(moe_out_, eout_, normed_, L.has_shared ? sout_ : nullptr, topk_idx_, topk_w_, slot_row_, N, W, L.top,
-                              L.experts, dt_, st)); ++launches;
-        RUN(nvllm_dyt_residual_norm(normed_, h_, moe_out_, L.n2b.alpha, L.n2b.w, L.n2b.b, next.alpha, next.w, next.b, N, W, dt_, st)); ++launches;
+                              L.experts, dt_, st)); ++launches; mk("moe_combine");
+        RUN(nvllm_dyt_residual_norm(normed_, h_, moe_out_, L.n2b.alpha, L.n2b.w, L.n2b.b, next.alpha, next.w, next.b, N, W, dt_, st)); ++launches; mk("dyt_residual_norm");
       }
       if (v.layer_tap != nullptr && !v.capturing)
         NVLLM_CUDA(cudaMemcpyAsync(v.layer_tap + r * static_cast<size_t>(N) * W, h_, static_cast<size_t>(N) * W * 4, cudaMemcpyDeviceToHost,
@@ -454,9 +467,10 @@ class Kosazen : public ModelImpl {
         head_rows_ = std::max(v.n_logit_rows, lim_.max_seqs);
         RUN(oalloc(&head_in_, static_cast<size_t>(head_rows_) * W));
       }
-      RUN(nvllm_gather_rows(head_in_, normed_, v.logit_rows, v.n_logit_rows, W, N, dt_, st)); ++launches;
+      RUN(nvllm_gather_rows(head_in_, normed_, v.logit_rows, v.n_logit_rows, W, N, dt_, st)); ++launches; mk("gather_rows");
       ++launches;
       RUN(nvllm_linear(v.logits, head_in_, head_, v.n_logit_rows, vocab_, W, W, W, vocab_, 1, 0, 0, 0, dt_, NVLLM_F32, st));
+      mk("head projection");
     }
     return 0;
   }

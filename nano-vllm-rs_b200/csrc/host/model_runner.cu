@@ -256,10 +256,11 @@ int nvllm_runner::forward_model(int N, int S) {
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
   v.capturing = cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone;
   v.layer_tap = layer_tap;
+  v.mark_ctx = this;
+  v.mark = [](void* ctx, const char* name) { static_cast<nvllm_runner*>(ctx)->mark(name); };
   mark("(step start)");
   RUN(model->forward(v));
   launches = model->launches;
-  mark("model forward");
   // next-token choice from the first min(rows, seqs) logit rows (by default row i is the last token of sequence i)
   const int rows = n_logit_rows < S ? n_logit_rows : S;
   if (rows > 0) { RUN(nvllm_argmax(tokens, nullptr, logits, rows, vshard, vshard, 0, NVLLM_F32, stream)); ++launches; mark("argmax"); }

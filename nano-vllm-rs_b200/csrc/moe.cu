@@ -1,6 +1,7 @@
 // moe.cu — routing side of a mixture-of-experts feed-forward, all on the device with static shapes (legal inside a CUDA
 // graph): softmax router with an additive selection bias, top-k choice, weight normalisation, identity experts, the
-// counting sort that groups (token, slot) assignments by expert into 32-row tiles for nvllm_linear_grouped, and the
+// counting sort that groups (token, slot) assignments by expert into 32-row tiles (nvllm_linear_grouped) or 128-row tiles
+// (nvllm_gemm_bf16_grouped), and the
 // weighted combine.  Everything here is f32 arithmetic.
 //
 //   s = softmax(z) over all router outputs (real experts first, then identity experts)
@@ -67,19 +68,19 @@ __global__ void __launch_bounds__(128) moe_route_kernel(int32_t* __restrict__ id
 }
 
 // Counting sort of the assignments by expert, one CTA.  Output layout: expert e owns rows [off[e], off[e] + cnt[e]) of the
-// grouped buffers, off[e] a multiple of 32 so that no 32-row tile spans two experts.
+// grouped buffers, off[e] a multiple of the tile height so that no tile spans two experts.
 //   row_token[r]  token whose activations row r reads (-1: padding)
 //   tile_expert[i] expert of tile i (-1: unused tile)
 //   slot_row[t*top + k] row of assignment (t, k), or -1 when it chose an identity expert
 __global__ void __launch_bounds__(1024) moe_sort_kernel(int32_t* __restrict__ row_token, int32_t* __restrict__ tile_expert,
                                                         int32_t* __restrict__ slot_row, const int32_t* __restrict__ idx,
-                                                        int n_assign, int top, int experts, int max_rows) {
+                                                        int n_assign, int top, int experts, int max_rows, int tile) {
   extern __shared__ int32_t sh[];
   int32_t* cnt = sh;             // [experts]
   int32_t* off = sh + experts;   // [experts + 1]
   for (int e = threadIdx.x; e < experts; e += blockDim.x) cnt[e] = 0;
   for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_token[r] = -1;
-  for (int i = threadIdx.x; i < max_rows / 32; i += blockDim.x) tile_expert[i] = -1;
+  for (int i = threadIdx.x; i < max_rows / tile; i += blockDim.x) tile_expert[i] = -1;
   __syncthreads();
   for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
     const int e = idx[a];
@@ -90,9 +91,9 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(int32_t* __restrict__ ro
     int o = 0;
     for (int e = 0; e < experts; ++e) {
       off[e] = o;
-      const int tiles = (cnt[e] + 31) / 32;
-      for (int i = 0; i < tiles; ++i) tile_expert[o / 32 + i] = e;
-      o += tiles * 32;
+      const int tiles = (cnt[e] + tile - 1) / tile;
+      for (int i = 0; i < tiles; ++i) tile_expert[o / tile + i] = e;
+      o += tiles * tile;
     }
     off[experts] = o;
   }
@@ -146,21 +147,22 @@ extern "C" int nvllm_moe_route(int32_t* topk_idx, float* topk_w, const float* lo
   return 0;
 }
 
-extern "C" int32_t nvllm_moe_max_rows(int32_t n_tokens, int32_t top, int32_t experts) {
-  const int64_t a = static_cast<int64_t>(n_tokens) * top + static_cast<int64_t>(experts) * 31;
-  return static_cast<int32_t>((a + 31) / 32 * 32);
+extern "C" int32_t nvllm_moe_max_rows(int32_t n_tokens, int32_t top, int32_t experts, int32_t tile_rows) {
+  if (tile_rows <= 0) return 0;
+  const int64_t a = static_cast<int64_t>(n_tokens) * top + static_cast<int64_t>(experts) * (tile_rows - 1);
+  return static_cast<int32_t>((a + tile_rows - 1) / tile_rows * tile_rows);
 }
 
 extern "C" int nvllm_moe_sort(int32_t* row_token, int32_t* tile_expert, int32_t* slot_row, const int32_t* topk_idx,
-                              int32_t n, int32_t top, int32_t experts, int32_t max_rows, void* stream) {
-  NVLLM_CHECK_ARG(n >= 0 && top > 0 && experts >= 0 && experts <= 8192 && max_rows % 32 == 0 &&
-                      max_rows >= nvllm_moe_max_rows(n, top, experts), NVLLM_ERR_ARG,
-                  "moe_sort: n=%d top=%d experts=%d max_rows=%d", n, top, experts, max_rows);
+                              int32_t n, int32_t top, int32_t experts, int32_t max_rows, int32_t tile_rows, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && top > 0 && experts >= 0 && experts <= 8192 && (tile_rows == 32 || tile_rows == 128) &&
+                      max_rows % tile_rows == 0 && max_rows >= nvllm_moe_max_rows(n, top, experts, tile_rows), NVLLM_ERR_ARG,
+                  "moe_sort: n=%d top=%d experts=%d max_rows=%d tile_rows=%d", n, top, experts, max_rows, tile_rows);
   if (n == 0) return 0;
   NVLLM_CHECK_ARG(row_token && tile_expert && slot_row && topk_idx, NVLLM_ERR_ARG, "moe_sort: NULL");
   const size_t smem = (2 * static_cast<size_t>(experts) + 1) * sizeof(int32_t);
   moe_sort_kernel<<<1, 1024, smem, static_cast<cudaStream_t>(stream)>>>(row_token, tile_expert, slot_row, topk_idx, n * top, top,
-                                                                      experts, max_rows);
+                                                                      experts, max_rows, tile_rows);
   NVLLM_LAUNCH_CHECK("moe_sort_kernel");
   return 0;
 }

@@ -336,15 +336,25 @@ def moe_route(logits, bias, top, scale):
     return idx, w
 
 
-def moe_sort(topk_idx, experts):
+def moe_sort(topk_idx, experts, tile_rows=32):
     n, top = topk_idx.shape
-    rows = _ffi.lib().nvllm_moe_max_rows(n, top, experts)
+    rows = _ffi.lib().nvllm_moe_max_rows(n, top, experts, tile_rows)
     dev = topk_idx.device
     row_token = torch.empty(rows, dtype=torch.int32, device=dev)
-    tile_expert = torch.empty(rows // 32, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(rows // tile_rows, dtype=torch.int32, device=dev)
     slot_row = torch.empty((n, top), dtype=torch.int32, device=dev)
-    check(_ffi.lib().nvllm_moe_sort(_p(row_token), _p(tile_expert), _p(slot_row), _p(topk_idx), n, top, experts, rows, _stream()))
+    check(_ffi.lib().nvllm_moe_sort(_p(row_token), _p(tile_expert), _p(slot_row), _p(topk_idx), n, top, experts, rows, tile_rows,
+                                    _stream()))
     return row_token, tile_expert, slot_row
+
+
+def gemm_bf16_grouped(x, w, tile_group, n, groups):
+    """x [max_rows, k] bf16 (rows already grouped in 128-row tiles), w [groups * n, k] -> [max_rows, n]."""
+    _need(x, torch.bfloat16, "x"); _need(w, torch.bfloat16, "w"); _need(tile_group, torch.int32, "tile_group")
+    out = torch.empty((x.shape[0], n), dtype=torch.bfloat16, device=x.device)
+    check(_ffi.lib().nvllm_gemm_bf16_grouped(_p(out), _p(x), _p(w), x.shape[0], n, x.shape[1], groups, x.stride(0), w.stride(0),
+                                             n, _p(tile_group), _stream()))
+    return out
 
 
 def moe_combine(expert_out, x, shared_out, topk_idx, topk_w, slot_row, experts):

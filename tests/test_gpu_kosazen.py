@@ -461,3 +461,26 @@ def test_trace_run_replays_a_schedule(cuda, tmp_path):
     rd = lambda n: np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
     for got, ref in ((rd(0), ra[[0, 39]]), (rd(1), ra[[68]]), (rd(2), np.stack([ra[69], rb[8]])), (rd(3), rb[[8]])):
         assert got.shape == ref.shape and rel_err(got, ref).max() < TOL["float32"]
+
+
+def test_grouped_tensor_core_gemm(cuda):
+    """128-row tiles, each against its own expert's weight block; unused tiles and padding rows are never read back."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(15)
+    n_tok, W, E, top, ff = 300, 128, 5, 2, 192
+    idx = torch.from_numpy(np.stack([rng.permutation(E + 1)[:top] for _ in range(n_tok)]).astype(np.int32)).to(cuda)   # E = identity
+    row_token, tile_expert, slot_row = ops.moe_sort(idx, E, tile_rows=128)
+    rt, te, sr = row_token.cpu().numpy(), tile_expert.cpu().numpy(), slot_row.cpu().numpy()
+    assert rt.size % 128 == 0 and te.size == rt.size // 128 and (te >= 0).sum() >= E
+    x = K.bf16_round(rng.standard_normal((n_tok, W)))
+    w = K.bf16_round(rng.standard_normal((E, ff, W)) / np.sqrt(W))
+    xg = torch.zeros((rt.size, W), dtype=torch.bfloat16, device=cuda)
+    xg[torch.from_numpy(rt >= 0).to(cuda)] = dev_t(x[rt[rt >= 0]], cuda, torch.bfloat16)
+    y = ops.gemm_bf16_grouped(xg, dev_t(w.reshape(E * ff, W), cuda, torch.bfloat16), tile_expert, ff, E).float().cpu().numpy()
+    idx_h = idx.cpu().numpy()
+    for t in range(0, n_tok, 7):
+        for k in range(top):
+            e = idx_h[t, k]
+            if e < E:
+                assert te[sr[t, k] // 128] == e
+                np.testing.assert_allclose(y[sr[t, k]], x[t] @ w[e].T, rtol=1e-2, atol=1e-2)
