@@ -53,7 +53,9 @@ def parse():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=None, help="override the workload model (qwen3-0.6b | qwen3-8b | qwen3-32b)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefix"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefix", "kosazen"],
+                    help="kosazen: prefill / decode throughput and a per-kernel roofline table of the Kosazen architecture "
+                         "(latent attention + mixture of experts) beside Qwen3 models of equal layer sizes, random weights")
     ap.add_argument("--seqs", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the in-run parity checks (profiling runs)")
@@ -698,6 +700,124 @@ def run_prefix(args, rank, world, local):
     return line, ok_blocks
 
 
+# ------------------------------------------------------------------------------------------------ Kosazen beside Qwen3
+# Layer sizes that resemble real latent-attention / mixture-of-experts models; the Qwen3 arm has the same width, head count,
+# head size and depth, and an MLP as wide as the experts one Kosazen token uses (top x ff + shared ff).
+ARCH_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, experts=64, ff=1408, top=6, shared_ff=2816,
+                  layers=2, vocab=32768, kv_heads=16),
+    "w4096": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, experts=32, ff=2048, top=4, shared_ff=4096,
+                  layers=2, vocab=32768, kv_heads=8),
+}
+
+
+def kosazen_config(z):
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+             "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["rot_dim"]}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "shared": {"ff": z["shared_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "identity": 0, "top": z["top"], "scale": 1.0}}
+    return {"architecture": "Kosazen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": mlp} for _ in range(z["layers"])]}
+
+
+def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
+    """Algorithmic work of the named launches of ONE layer at n_tok tokens (context ctx per sequence): {name: (flop, bytes)}."""
+    W, H, L = z["width"], z["heads"], ctx
+    pairs = n_tok * ((L + 1) / 2 if not decode else L)   # (query, key) pairs per head
+    out = {}
+    if arch == "kosazen":
+        r, rd, d, vd, E, ff, top, sff = z["kv_rank"], z["rot_dim"], z["dim"], z["vdim"], z["experts"], z["ff"], z["top"], z["shared_ff"]
+        out["latent_attention"] = (2 * pairs * H * (2 * r + rd), (n_tok // max(1, L) if not decode else n_tok) * L * (r + rd) * 2 + n_tok * H * (2 * r + rd) * 4)
+        out["q + compressed kv projection"] = (2 * n_tok * W * (H * (d + rd) + r + rd), 2 * W * (H * (d + rd) + r + rd))
+        out["attention output projection"] = (2 * n_tok * W * H * vd, 2 * W * H * vd)
+        used = min(E, n_tok * top)
+        out["expert gate_up grouped GEMM"] = (2 * n_tok * top * W * 2 * ff, 2 * used * 2 * ff * W)
+        out["expert down grouped GEMM"] = (2 * n_tok * top * W * ff, 2 * used * ff * W)
+        out["shared gate_up projection"] = (2 * n_tok * W * 2 * sff, 2 * 2 * sff * W)
+        out["shared down projection"] = (2 * n_tok * W * sff, 2 * sff * W)
+    else:
+        D, Hkv, I = 128, z["kv_heads"], z["top"] * z["ff"] + z["shared_ff"]
+        att = "paged_decode_attention" if decode else "prefill_attention"
+        out[att] = (4 * pairs * H * D, (n_tok * L if decode else n_tok) * Hkv * D * 2 * 2)
+        out["qkv_proj GEMM"] = (2 * n_tok * W * (H + 2 * Hkv) * D, 2 * W * (H + 2 * Hkv) * D)
+        out["o_proj GEMM"] = (2 * n_tok * W * H * D, 2 * W * H * D)
+        out["gate_up_proj GEMM + SiLU*mul"] = (2 * n_tok * W * 2 * I, 2 * 2 * I * W)
+        out["down_proj GEMM"] = (2 * n_tok * W * I, 2 * I * W)
+    return {k: max(f / (tf * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}   # roofline microseconds
+
+
+def run_arch_compare(args):
+    import torch
+    from nano_vllm_rs_b200 import engine as E
+    hbm, _ = peaks()
+    tf, _ = tensor_peak()
+    n_prompts, plen, dec_b = 8, 1024, args.seqs or 64
+    rng = __import__("numpy").random.default_rng(0)
+    result = {"workload": "kosazen-vs-qwen3", "data": "synthetic", "dtype": "bf16", "prefill": f"{n_prompts} x {plen} tokens per step",
+              "decode": f"{dec_b} sequences at context {plen}+", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf}, "sizes": {}}
+    for name, z in ARCH_SIZES.items():
+        result["sizes"][name] = {}
+        for arch in ("kosazen", "qwen3"):
+            progress(f"{name} {arch}: building the engine (random weights)")
+            blocks = dec_b * (plen + 256) // 256 + 8
+            common = dict(kvcache_block_size=256, num_kvcache_blocks=blocks, max_num_seqs=dec_b,
+                          max_num_batched_tokens=n_prompts * plen, max_model_len=plen + 256)
+            if arch == "kosazen":
+                cfg = E.Config(model_config=kosazen_config(z), **common)
+            else:
+                cfg = E.Config("qwen3-0.6b", vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=z["layers"],
+                               intermediate_size=z["top"] * z["ff"] + z["shared_ff"], num_attention_heads=z["heads"],
+                               num_key_value_heads=z["kv_heads"], tie_word_embeddings=0, max_position_embeddings=4096, **common)
+            eng = E.LLMEngine(cfg, seed=7, std=0.02)
+            sp = E.SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 4, ignore_eos=True)
+            for _ in range(dec_b):
+                eng.add_request(rng.integers(0, z["vocab"], plen).tolist(), sp)
+            # prefill: dec_b / n_prompts steps of n_prompts x plen tokens; the first is warm-up, one is profiled per launch
+            times, prof_prefill = [], {}
+            for i in range(dec_b // n_prompts):
+                if i == 1:
+                    eng.model_runner.profile(True)
+                torch.cuda.synchronize(); t0 = time.perf_counter()
+                is_prefill, ns, nt = eng.step()
+                torch.cuda.synchronize(); dt = time.perf_counter() - t0
+                assert is_prefill and nt == n_prompts * plen, (is_prefill, ns, nt)
+                if i == 1:
+                    eng.model_runner.profile(False)
+                    prof_prefill = eng.model_runner.profile_report()
+                elif i > 1:
+                    times.append(dt)
+            prefill_tok_s = n_prompts * plen / (sum(times) / len(times))
+            # decode: first step of the bucket runs eagerly (profiled), then graph replays between CUDA events
+            eng.model_runner.profile(True)
+            eng.step()
+            eng.model_runner.profile(False)
+            prof_decode = eng.model_runner.profile_report()
+            for _ in range(max(3, args.warmup)):
+                eng.step()
+            ms = eng.model_runner.replay_decode(args.steps)
+            decode_tok_s = dec_b * args.steps / (ms / 1e3)
+
+            def table(prof, n_tok, decode):
+                roof = kernel_rooflines(z, arch, n_tok, plen, decode, hbm, tf)
+                rows = {}
+                for k, (calls, us) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
+                    per = us / max(1, calls)
+                    rows[k] = {"launches": calls, "us_per_launch": round(per, 2)}
+                    if k in roof:
+                        rows[k]["roofline_us"] = round(roof[k], 2)
+                        rows[k]["fraction_of_roofline"] = round(roof[k] / per, 3)
+                return rows
+
+            result["sizes"][name][arch] = {
+                "prefill_tokens_per_s": round(prefill_tok_s), "decode_tokens_per_s": round(decode_tok_s),
+                "decode_ms_per_step": round(ms / args.steps, 3),
+                "prefill_kernels": table(prof_prefill, n_prompts * plen, False), "decode_kernels": table(prof_decode, dec_b, True)}
+            progress(f"{name} {arch}: prefill {prefill_tok_s:,.0f} tok/s, decode {decode_tok_s:,.0f} tok/s")
+            del eng
+            torch.cuda.empty_cache()
+    return result
+
+
 def arm_watchdog():
     """A bench run that stops making progress (a rank waiting for a peer that died, a kernel that never returns) must not
     sit there until someone else's limit kills it without a trace.  A daemon thread watches the time since the last
@@ -745,6 +865,10 @@ def main():
     torch.cuda.set_device(local)
     lib = E.lib()
     assert lib.nvllm_device_ok() == 1, "no sm_100 device: the product path has no fallback"
+    if args.workload == "kosazen":
+        assert world == 1, "--workload kosazen is a one-GPU comparison"
+        print(json.dumps(run_arch_compare(args)), flush=True)
+        sys.exit(0)
     if args.workload == "prefix":
         line, ok = run_prefix(args, rank, world, local)
         print(json.dumps(line), flush=True)

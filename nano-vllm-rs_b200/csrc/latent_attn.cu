@@ -180,6 +180,161 @@ int launch_attn(const AttnArgs& a, cudaStream_t st) {
   return 0;
 }
 
+
+// ---- tensor-core variant (bf16 operands) -------------------------------------------------------------------------------
+// With the key map folded into the query, all heads of a token score against the SAME cache rows: the heads are the M
+// dimension of the matrix products.  CTA = one query token x 16 heads, 4 warps, key tiles of 64 cache rows staged in shared
+// memory (bf16, rows padded against bank conflicts):
+//   S[16 x 64]  = Q[16 x (kv_rank + rot_dim)] . K^T      each warp 16 keys, mma.sync m16n8k16, f32 accumulate
+//   online softmax in f32 through shared memory (row max / sum / rescale factor), P rounded to bf16
+//   O[16 x kv_rank] += P[16 x 64] . C[64 x kv_rank]      each warp a quarter of the columns, C read with ldmatrix.trans
+// Decoding is bound by reading the cache once per token; prompt portions re-read the tile per token from L2.
+constexpr int kMmaKeys = 64, kPsStride = 72, kSsStride = 68;
+
+template <int NT2>  // the warp owns NT2 * 16 output columns; kv_rank padded to NT2 * 64
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, int DPS, int DP16) {
+  extern __shared__ __align__(16) uint8_t smraw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);          // [16][DPS]
+  bf16* Ks = Qs + 16 * DPS;                           // [64][DPS]
+  bf16* Ps = Ks + kMmaKeys * DPS;                     // [16][kPsStride]
+  float* Ss = reinterpret_cast<float*>(Ps + 16 * kPsStride);  // [16][kSsStride]
+  float* m_s = Ss + 16 * kSsStride;
+  float* l_s = m_s + 16;
+  float* c_s = l_s + 16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int t = blockIdx.x, hbase = blockIdx.y * 16;
+  const int seq = a.tok_seq[t];
+  const int nkeys = static_cast<int>(a.positions[t]) + 1;
+  const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
+  const int D = a.kv_rank + a.rot_dim;
+  constexpr int RC = NT2 * 16;
+  // zero everything once (padding rows / columns stay zero), then the queries: [folded q (f32 -> bf16) | rotated part]
+  for (int e = tid; e < (16 + kMmaKeys) * DPS / 8; e += 128) reinterpret_cast<uint4*>(Qs)[e] = make_uint4(0, 0, 0, 0);
+  if (tid < 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
+  __syncthreads();
+  for (int e = tid; e < 16 * D; e += 128) {
+    const int r = e / D, d = e - r * D, h = hbase + r;
+    if (h >= a.heads) continue;
+    float v;
+    if (d < a.kv_rank) v = a.q_abs[static_cast<int64_t>(t) * a.ldqa + static_cast<int64_t>(h) * a.kv_rank + d];
+    else v = __bfloat162float(static_cast<const bf16*>(a.q)[static_cast<int64_t>(t) * a.ldq + static_cast<int64_t>(h) * (a.dim + a.rot_dim) + a.dim + (d - a.kv_rank)]);
+    Qs[r * DPS + d] = __float2bfloat16_rn(v);
+  }
+  float acc[2 * NT2][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NT2; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const int vec_per_row = static_cast<int>(a.cache_row / 8);   // cache rows are padded to 8 elements (zeros)
+  for (int j0 = 0; j0 < nkeys; j0 += kMmaKeys) {
+    __syncthreads();   // previous tile fully consumed (and the queries written, first time round)
+    for (int e = tid; e < kMmaKeys * vec_per_row; e += 128) {
+      const int jj = e / vec_per_row, v = e - jj * vec_per_row, j = j0 + jj;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (j < nkeys) {
+        const int32_t blk = table[j / a.block_size];
+        if (blk >= 0)
+          val = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(a.cache) +
+                                                (static_cast<int64_t>(blk) * a.block_size + j % a.block_size) * a.cache_row + v * 8);
+      }
+      *reinterpret_cast<uint4*>(Ks + jj * DPS + v * 8) = val;
+    }
+    __syncthreads();
+    {  // scores of this warp's 16 keys
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const int krow = 16 * warp;
+      for (int ks = 0; ks < DP16 / 16; ++ks) {
+        uint32_t af[4], bq[4];
+        ldmatrix_x4(af, smem_u32(Qs + (lane & 15) * DPS + ks * 16 + (lane >> 4) * 8));
+        ldmatrix_x4(bq, smem_u32(Ks + (krow + (lane & 7) + 8 * (lane >> 4)) * DPS + ks * 16 + 8 * ((lane >> 3) & 1)));
+        mma_bf16_16816(s[0], af, bq[0], bq[1]);
+        mma_bf16_16816(s[1], af, bq[2], bq[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int col = krow + nt * 8 + 2 * t4;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int j = j0 + col + c;
+          const bool ok = j < nkeys && table[j / a.block_size] >= 0;
+          Ss[g * kSsStride + col + c] = ok ? s[nt][c] * a.scale : -INFINITY;
+          Ss[(g + 8) * kSsStride + col + c] = ok ? s[nt][2 + c] * a.scale : -INFINITY;
+        }
+      }
+    }
+    __syncthreads();
+    {  // online softmax: warp w owns rows 4w..4w+3, 8 lanes per row, 8 keys per lane
+      const int row = 4 * warp + (lane >> 3), sub = lane & 7;
+      float sv[8], mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { sv[i] = Ss[row * kSsStride + sub * 8 + i]; mx = fmaxf(mx, sv[i]); }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_old = m_s[row], m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float p = (sv[i] == -INFINITY) ? 0.f : expf(sv[i] - m_new);
+        sum += p;
+        Ps[row * kPsStride + sub * 8 + i] = __float2bfloat16_rn(p);
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncwarp();
+      if (sub == 0) {
+        const float corr = (m_new == -INFINITY || m_old == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f) : expf(m_old - m_new);
+        c_s[row] = corr;
+        l_s[row] = l_s[row] * corr + sum;
+        m_s[row] = m_new;
+      }
+    }
+    __syncthreads();
+    {  // O += P . C over this warp's RC columns
+      const float cg = c_s[g], cg8 = c_s[g + 8];
+#pragma unroll
+      for (int i = 0; i < 2 * NT2; ++i) { acc[i][0] *= cg; acc[i][1] *= cg; acc[i][2] *= cg8; acc[i][3] *= cg8; }
+#pragma unroll
+      for (int kk = 0; kk < kMmaKeys / 16; ++kk) {
+        uint32_t pf[4];
+        ldmatrix_x4(pf, smem_u32(Ps + (lane & 15) * kPsStride + kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+        for (int p2 = 0; p2 < NT2; ++p2) {
+          uint32_t bv[4];
+          ldmatrix_x4_trans(bv, smem_u32(Ks + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DPS + warp * RC + p2 * 16 + 8 * (lane >> 4)));
+          mma_bf16_16816(acc[2 * p2], pf, bv[0], bv[1]);
+          mma_bf16_16816(acc[2 * p2 + 1], pf, bv[2], bv[3]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  bf16* out = static_cast<bf16*>(a.out) + static_cast<int64_t>(t) * a.ldo;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = g + 8 * half, h = hbase + r;
+    if (h >= a.heads) continue;
+    const float l = l_s[r], inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2 * NT2; ++nt)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int col = warp * RC + nt * 8 + 2 * t4 + c;
+        if (col < a.kv_rank) out[static_cast<int64_t>(h) * a.kv_rank + col] = __float2bfloat16_rn(acc[nt][2 * half + c] * inv);
+      }
+  }
+}
+
+template <int NT2>
+int launch_attn_mma(const AttnArgs& a, cudaStream_t st) {
+  const int D = a.kv_rank + a.rot_dim, DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 64;
+  (void)D;
+  const int DPS = (DP16 > RP ? DP16 : RP) + 8;
+  const size_t smem = static_cast<size_t>(16 + kMmaKeys) * DPS * 2 + 16 * kPsStride * 2 + (16 * kSsStride + 48) * 4;
+  NVLLM_SMEM_ATTR_ONCE((latent_attn_mma_kernel<NT2>), 200 * 1024);
+  dim3 grid(a.n, (a.heads + 15) / 16);
+  latent_attn_mma_kernel<NT2><<<grid, 128, smem, st>>>(a, DPS, DP16);
+  NVLLM_LAUNCH_CHECK("latent_attn_mma_kernel");
+  return 0;
+}
+
 template <typename T>
 int dispatch_attn(const AttnArgs& a, cudaStream_t st) {
   if (a.kv_rank <= 128) return launch_attn<T, 4>(a, st);
@@ -238,5 +393,14 @@ extern "C" int nvllm_latent_attention(void* out, int64_t ldo, const float* q_abs
   const AttnArgs a{out, ldo, q_abs, ldqa, q, ldq, tok_seq, positions, block_tables, table_cap, block_size, cache, cache_row,
                    n, heads, dim, rot_dim, kv_rank, scale};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // bf16 caches with a 16-byte row pitch and kv_rank <= 512 run on the tensor cores (NVLLM_LATENT_MMA=0: the CUDA-core kernel)
+  const int dp16 = (static_cast<int>(cache_row) + 15) / 16 * 16;
+  if (dtype == NVLLM_BF16 && knobs().latent_mma != 0 && kv_rank <= 512 && cache_row % 8 == 0 && dp16 <= 1024 &&
+      (reinterpret_cast<uintptr_t>(cache) & 15u) == 0) {
+    if (kv_rank <= 64) return launch_attn_mma<1>(a, st);
+    if (kv_rank <= 128) return launch_attn_mma<2>(a, st);
+    if (kv_rank <= 256) return launch_attn_mma<4>(a, st);
+    return launch_attn_mma<8>(a, st);
+  }
   return dtype == NVLLM_BF16 ? dispatch_attn<bf16>(a, st) : dispatch_attn<float>(a, st);
 }
