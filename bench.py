@@ -787,11 +787,14 @@ def run_arch_compare(args):
                 elif i > 1:
                     times.append(dt)
             prefill_tok_s = n_prompts * plen / (sum(times) / len(times))
-            # decode: first step of the bucket runs eagerly (profiled), then graph replays between CUDA events
+            # decode: warm eager steps, one of them profiled per launch; then graph replays between CUDA events
+            eng.model_runner.set_eager(True)
+            eng.step(); eng.step()
             eng.model_runner.profile(True)
             eng.step()
             eng.model_runner.profile(False)
             prof_decode = eng.model_runner.profile_report()
+            eng.model_runner.set_eager(False)
             for _ in range(max(3, args.warmup)):
                 eng.step()
             ms = eng.model_runner.replay_decode(args.steps)

@@ -182,6 +182,9 @@ void* nvllm_runner_stream(nvllm_runner* r);
  * returns the full length. */
 int nvllm_runner_profile(nvllm_runner* r, int32_t enable);
 int64_t nvllm_runner_profile_report(nvllm_runner* r, char* h_buf, size_t cap);
+/* Switches CUDA-graph replay of decode steps off (1) or back on (0) for the steps that follow (profiling eager steps of a
+ * runner that otherwise replays graphs). */
+int nvllm_runner_set_eager(nvllm_runner* r, int32_t eager);
 /* Number of kernels launched by the last execute (decode graph node count, or eager launches). */
 int64_t nvllm_runner_last_launches(const nvllm_runner* r);
 /* Device pointers of layer `layer`'s K / V cache and the layout in use (tests). */

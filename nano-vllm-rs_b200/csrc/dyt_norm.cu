@@ -19,6 +19,42 @@ template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = _
 
 struct DytParams { const float* alpha; const float* w; const float* b; };
 
+// 8 bf16 values <-> one 16-byte vector
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+// bf16 rows whose length is a multiple of 8: 16-byte vectors (the residual as two float4)
+__global__ void dyt_residual_norm_vec8_kernel(bf16* __restrict__ out, float* __restrict__ h, const bf16* __restrict__ y,
+                                              DytParams post, DytParams pre, int64_t total8, int hidden8) {
+  const float a_post = y ? *post.alpha : 0.f, a_pre = out ? *pre.alpha : 0.f;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total8;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % hidden8) * 8;
+    float v[8];
+    *reinterpret_cast<float4*>(v) = reinterpret_cast<const float4*>(h)[2 * i];
+    *reinterpret_cast<float4*>(v + 4) = reinterpret_cast<const float4*>(h)[2 * i + 1];
+    if (y) {
+      float yv[8];
+      unpack8(reinterpret_cast<const uint4*>(y)[i], yv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += tanhf(a_post * yv[j]) * post.w[c + j] + post.b[c + j];
+      reinterpret_cast<float4*>(h)[2 * i] = *reinterpret_cast<float4*>(v);
+      reinterpret_cast<float4*>(h)[2 * i + 1] = *reinterpret_cast<float4*>(v + 4);
+    }
+    if (out) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = tanhf(a_pre * v[j]) * pre.w[c + j] + pre.b[c + j];
+      reinterpret_cast<uint4*>(out)[i] = pack8(o);
+    }
+  }
+}
+
 template <typename T>
 __global__ void dyt_residual_norm_kernel(T* __restrict__ out, float* __restrict__ h, const T* __restrict__ y, DytParams post,
                                          DytParams pre, int64_t total, int hidden) {
@@ -45,6 +81,19 @@ __global__ void embedding_f32_kernel(float* __restrict__ h, const T* __restrict_
     int64_t id = ids[r];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     h[i] = ldf(table + id * hidden + c);
+  }
+}
+
+// rows whose byte length is a multiple of 16: plain 16-byte copies
+__global__ void gather_rows_vec_kernel(uint4* __restrict__ out, const uint4* __restrict__ x, const int32_t* __restrict__ rows, int n,
+                                       int vecs, int n_src) {
+  const int64_t total = static_cast<int64_t>(n) * vecs;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vecs, c = i - r * vecs;
+    int32_t s = rows[r];
+    s = s < 0 ? 0 : (s >= n_src ? n_src - 1 : s);
+    out[i] = x[static_cast<int64_t>(s) * vecs + c];
   }
 }
 
@@ -84,7 +133,10 @@ extern "C" int nvllm_dyt_residual_norm(void* out, float* h, const void* y, const
   const int64_t total = static_cast<int64_t>(n) * hidden;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const DytParams post{post_alpha, post_w, post_b}, pre{pre_alpha, pre_w, pre_b};
-  if (dtype == NVLLM_BF16)
+  if (dtype == NVLLM_BF16 && hidden % 8 == 0 && aligned16(h) && aligned16(out) && aligned16(y))
+    dyt_residual_norm_vec8_kernel<<<blocks_for(total / 8), 256, 0, st>>>(static_cast<bf16*>(out), h, static_cast<const bf16*>(y), post, pre,
+                                                                          total / 8, hidden / 8);
+  else if (dtype == NVLLM_BF16)
     dyt_residual_norm_kernel<bf16><<<blocks_for(total), 256, 0, st>>>(static_cast<bf16*>(out), h, static_cast<const bf16*>(y), post, pre, total, hidden);
   else
     dyt_residual_norm_kernel<float><<<blocks_for(total), 256, 0, st>>>(static_cast<float*>(out), h, static_cast<const float*>(y), post, pre, total, hidden);
@@ -116,6 +168,13 @@ extern "C" int nvllm_gather_rows(void* out, const void* x, const int32_t* rows, 
   NVLLM_CHECK_ARG(out && x && rows, NVLLM_ERR_ARG, "gather_rows: NULL");
   const int64_t total = static_cast<int64_t>(n) * hidden;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t row_bytes = static_cast<int64_t>(hidden) * (dtype == NVLLM_BF16 ? 2 : 4);
+  if (row_bytes % 16 == 0 && aligned16(out) && aligned16(x)) {
+    const int vecs = static_cast<int>(row_bytes / 16);
+    gather_rows_vec_kernel<<<blocks_for(static_cast<int64_t>(n) * vecs), 256, 0, st>>>(static_cast<uint4*>(out), static_cast<const uint4*>(x), rows, n, vecs, n_src);
+    NVLLM_LAUNCH_CHECK("gather_rows_vec_kernel");
+    return 0;
+  }
   if (dtype == NVLLM_BF16)
     gather_rows_kernel<bf16><<<blocks_for(total), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(x), rows, n, hidden, n_src);
   else

@@ -414,7 +414,18 @@ class Kosazen : public ModelImpl {
                                L.rot_dims, lim_.max_positions, N, L.heads, L.dim, L.rot_dim, L.kv_rank, cache_[r], L.cache_row(),
                                v.slots, dt_, st)); ++launches; mk("latent_prepare");
       // fold the key up-projection into the query: qa[t, h, :] = Uk_h^T q[t, h, :dim]  (f32)
-      if (L.dim > 0) {
+      // Per-head projections: with many tokens every head is a tensor-core GEMM of its own (views into the packed
+      // activations); with few (decoding) one batched launch of the tile kernel beats `heads` launch latencies.
+      const bool head_gemms = dt_ == NVLLM_BF16 && N >= 512 && L.dim % 64 == 0 && L.kv_rank % 64 == 0 && L.vdim % 8 == 0 &&
+                              qh % 8 == 0 && ldqd % 8 == 0;
+      if (L.dim > 0 && head_gemms) {
+        for (int hh = 0; hh < L.heads; ++hh) {
+          RUN(nvllm_gemm_bf16(q_abs_ + static_cast<size_t>(hh) * L.kv_rank, qd + static_cast<size_t>(hh) * qh * 2,
+                              static_cast<uint8_t*>(L.ukT) + static_cast<size_t>(hh) * L.kv_rank * L.dim * 2, N, L.kv_rank, L.dim, ldqd,
+                              L.dim, HR, NVLLM_F32, nullptr, 0, st)); ++launches;
+        }
+        mk("q absorb (per-head GEMMs)");
+      } else if (L.dim > 0) {
         RUN(nvllm_linear(q_abs_, qd_, L.ukT, N, L.kv_rank, L.dim, ldqd, L.dim, HR, L.heads, qh, static_cast<int64_t>(L.kv_rank) * L.dim,
                          L.kv_rank, dt_, NVLLM_F32, st)); ++launches; mk("q absorb (per-head linear)");
       } else {
@@ -423,8 +434,18 @@ class Kosazen : public ModelImpl {
       RUN(nvllm_latent_attention(o_lat_, HR, q_abs_, HR, qd_, ldqd, v.tok_seq, v.positions, v.tables, v.table_cap, lim_.block_size,
                                  cache_[r], L.cache_row(), N, L.heads, L.dim, L.rot_dim, L.kv_rank, L.scale, dt_, st)); ++launches; mk("latent_attention");
       // values: per head Uv_h applied to the attended latent, then the output projection
-      RUN(nvllm_linear(attn_, o_lat_, L.uv, N, L.vdim, L.kv_rank, HR, L.kv_rank, HV, L.heads, L.kv_rank,
-                       static_cast<int64_t>(L.vdim) * L.kv_rank, L.vdim, dt_, act_dt, st)); ++launches; mk("value up-projection (per-head linear)");
+      if (head_gemms) {
+        for (int hh = 0; hh < L.heads; ++hh) {
+          RUN(nvllm_gemm_bf16(static_cast<uint8_t*>(attn_) + static_cast<size_t>(hh) * L.vdim * 2,
+                              static_cast<uint8_t*>(o_lat_) + static_cast<size_t>(hh) * L.kv_rank * 2,
+                              static_cast<uint8_t*>(L.uv) + static_cast<size_t>(hh) * L.vdim * L.kv_rank * 2, N, L.vdim, L.kv_rank, HR,
+                              L.kv_rank, HV, NVLLM_BF16, nullptr, 0, st)); ++launches;
+        }
+        mk("value up-projection (per-head GEMMs)");
+      } else {
+        RUN(nvllm_linear(attn_, o_lat_, L.uv, N, L.vdim, L.kv_rank, HR, L.kv_rank, HV, L.heads, L.kv_rank,
+                         static_cast<int64_t>(L.vdim) * L.kv_rank, L.vdim, dt_, act_dt, st)); ++launches; mk("value up-projection (per-head linear)");
+      }
       RUN(lin(proj_, attn_, L.o, W, static_cast<int>(HV), HV, W, act_dt, "attention output projection"));
       if (!L.has_mlp) {
         RUN(nvllm_dyt_residual_norm(normed_, h_, proj_, L.n1b.alpha, L.n1b.w, L.n1b.b, next.alpha, next.w, next.b, N, W, dt_, st)); ++launches; mk("dyt_residual_norm");

@@ -917,6 +917,11 @@ int64_t nvllm_runner_profile_report(nvllm_runner* r, char* h_buf, size_t cap) {
   }
   return static_cast<int64_t>(out.size());
 }
+int nvllm_runner_set_eager(nvllm_runner* r, int32_t eager) {
+  NVLLM_CHECK_ARG(r, NVLLM_ERR_ARG, "runner_set_eager: NULL");
+  r->cfg.enforce_eager = eager != 0;
+  return 0;
+}
 int64_t nvllm_runner_last_launches(const nvllm_runner* r) { return r ? r->last_launches : 0; }
 int nvllm_runner_kv_cache(nvllm_runner* r, int32_t layer, void** k_cache, void** v_cache, nvllm_kv_layout* layout) {
   NVLLM_CHECK_ARG(r && !r->model, NVLLM_ERR_STATE, "runner_kv_cache: built-in Qwen3 runner only");

@@ -195,8 +195,8 @@ template <int NT2>  // the warp owns NT2 * 16 output columns; kv_rank padded to 
 __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, int DPS, int DP16) {
   extern __shared__ __align__(16) uint8_t smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);          // [16][DPS]
-  bf16* Ks = Qs + 16 * DPS;                           // [64][DPS]
-  bf16* Ps = Ks + kMmaKeys * DPS;                     // [16][kPsStride]
+  bf16* Kbuf = Qs + 16 * DPS;                         // 2 x [64][DPS]: the next tile lands while this one is used
+  bf16* Ps = Kbuf + 2 * kMmaKeys * DPS;               // [16][kPsStride]
   float* Ss = reinterpret_cast<float*>(Ps + 16 * kPsStride);  // [16][kSsStride]
   float* m_s = Ss + 16 * kSsStride;
   float* l_s = m_s + 16;
@@ -208,10 +208,27 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
   const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
   const int D = a.kv_rank + a.rot_dim;
   constexpr int RC = NT2 * 16;
-  // zero everything once (padding rows / columns stay zero), then the queries: [folded q (f32 -> bf16) | rotated part]
-  for (int e = tid; e < (16 + kMmaKeys) * DPS / 8; e += 128) reinterpret_cast<uint4*>(Qs)[e] = make_uint4(0, 0, 0, 0);
+  const int vec_per_row = static_cast<int>(a.cache_row / 8);   // cache rows are padded to 8 elements (zeros)
+  // zero everything once (padding rows / columns stay zero)
+  for (int e = tid; e < (16 + 2 * kMmaKeys) * DPS / 8; e += 128) reinterpret_cast<uint4*>(Qs)[e] = make_uint4(0, 0, 0, 0);
   if (tid < 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
   __syncthreads();
+  // two threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
+  // the sequence's keys and for missing blocks)
+  auto prefetch = [&](int j0, bf16* Ks) {
+    const int jj = tid >> 1, j = j0 + jj;
+    const bf16* src = static_cast<const bf16*>(a.cache);
+    int bytes = 0;
+    if (j < nkeys) {
+      const int32_t blk = table[j / a.block_size];
+      if (blk >= 0) { src += (static_cast<int64_t>(blk) * a.block_size + j % a.block_size) * a.cache_row; bytes = 16; }
+    }
+    const uint32_t dst = smem_u32(Ks + jj * DPS);
+    for (int v = tid & 1; v < vec_per_row; v += 2) cp_async_16(dst + v * 16, src + (bytes ? v * 8 : 0), bytes);
+    cp_async_commit();
+  };
+  prefetch(0, Kbuf);
+  // the queries: [folded q (f32 -> bf16) | rotated part]
   for (int e = tid; e < 16 * D; e += 128) {
     const int r = e / D, d = e - r * D, h = hbase + r;
     if (h >= a.heads) continue;
@@ -223,28 +240,26 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
   float acc[2 * NT2][4];
 #pragma unroll
   for (int i = 0; i < 2 * NT2; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  const int vec_per_row = static_cast<int>(a.cache_row / 8);   // cache rows are padded to 8 elements (zeros)
-  for (int j0 = 0; j0 < nkeys; j0 += kMmaKeys) {
-    __syncthreads();   // previous tile fully consumed (and the queries written, first time round)
-    for (int e = tid; e < kMmaKeys * vec_per_row; e += 128) {
-      const int jj = e / vec_per_row, v = e - jj * vec_per_row, j = j0 + jj;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (j < nkeys) {
-        const int32_t blk = table[j / a.block_size];
-        if (blk >= 0)
-          val = *reinterpret_cast<const uint4*>(static_cast<const bf16*>(a.cache) +
-                                                (static_cast<int64_t>(blk) * a.block_size + j % a.block_size) * a.cache_row + v * 8);
-      }
-      *reinterpret_cast<uint4*>(Ks + jj * DPS + v * 8) = val;
+  int buf = 0;
+  for (int j0 = 0; j0 < nkeys; j0 += kMmaKeys, buf ^= 1) {
+    bf16* Ks = Kbuf + buf * kMmaKeys * DPS;
+    if (j0 + kMmaKeys < nkeys) {
+      prefetch(j0 + kMmaKeys, Kbuf + (buf ^ 1) * kMmaKeys * DPS);   // that buffer's last readers passed the barrier below
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    __syncthreads();
+    __syncthreads();   // this tile (and, first time round, the queries) visible to all warps
     {  // scores of this warp's 16 keys
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       const int krow = 16 * warp;
+      const uint32_t qa = smem_u32(Qs + (lane & 15) * DPS + (lane >> 4) * 8);
+      const uint32_t ka = smem_u32(Ks + (krow + (lane & 7) + 8 * (lane >> 4)) * DPS + 8 * ((lane >> 3) & 1));
+#pragma unroll 4
       for (int ks = 0; ks < DP16 / 16; ++ks) {
         uint32_t af[4], bq[4];
-        ldmatrix_x4(af, smem_u32(Qs + (lane & 15) * DPS + ks * 16 + (lane >> 4) * 8));
-        ldmatrix_x4(bq, smem_u32(Ks + (krow + (lane & 7) + 8 * (lane >> 4)) * DPS + ks * 16 + 8 * ((lane >> 3) & 1)));
+        ldmatrix_x4(af, qa + ks * 32);
+        ldmatrix_x4(bq, ka + ks * 32);
         mma_bf16_16816(s[0], af, bq[0], bq[1]);
         mma_bf16_16816(s[1], af, bq[2], bq[3]);
       }
@@ -269,13 +284,14 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float m_old = m_s[row], m_new = fmaxf(m_old, mx);
-      float sum = 0.f;
+      float sum = 0.f, pv[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float p = (sv[i] == -INFINITY) ? 0.f : expf(sv[i] - m_new);
-        sum += p;
-        Ps[row * kPsStride + sub * 8 + i] = __float2bfloat16_rn(p);
+        pv[i] = (sv[i] == -INFINITY) ? 0.f : expf(sv[i] - m_new);
+        sum += pv[i];
       }
+      *reinterpret_cast<uint4*>(Ps + row * kPsStride + sub * 8) =
+          make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]), pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       __syncwarp();
@@ -304,8 +320,8 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
         }
       }
     }
+    __syncthreads();   // tile, P and the row factors are free again
   }
-  __syncthreads();
   bf16* out = static_cast<bf16*>(a.out) + static_cast<int64_t>(t) * a.ldo;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
@@ -327,8 +343,8 @@ int launch_attn_mma(const AttnArgs& a, cudaStream_t st) {
   const int D = a.kv_rank + a.rot_dim, DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 64;
   (void)D;
   const int DPS = (DP16 > RP ? DP16 : RP) + 8;
-  const size_t smem = static_cast<size_t>(16 + kMmaKeys) * DPS * 2 + 16 * kPsStride * 2 + (16 * kSsStride + 48) * 4;
-  NVLLM_SMEM_ATTR_ONCE((latent_attn_mma_kernel<NT2>), 200 * 1024);
+  const size_t smem = static_cast<size_t>(16 + 2 * kMmaKeys) * DPS * 2 + 16 * kPsStride * 2 + (16 * kSsStride + 48) * 4;
+  NVLLM_SMEM_ATTR_ONCE((latent_attn_mma_kernel<NT2>), 220 * 1024);
   dim3 grid(a.n, (a.heads + 15) / 16);
   latent_attn_mma_kernel<NT2><<<grid, 128, smem, st>>>(a, DPS, DP16);
   NVLLM_LAUNCH_CHECK("latent_attn_mma_kernel");
@@ -395,7 +411,7 @@ extern "C" int nvllm_latent_attention(void* out, int64_t ldo, const float* q_abs
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // bf16 caches with a 16-byte row pitch and kv_rank <= 512 run on the tensor cores (NVLLM_LATENT_MMA=0: the CUDA-core kernel)
   const int dp16 = (static_cast<int>(cache_row) + 15) / 16 * 16;
-  if (dtype == NVLLM_BF16 && knobs().latent_mma != 0 && kv_rank <= 512 && cache_row % 8 == 0 && dp16 <= 1024 &&
+  if (dtype == NVLLM_BF16 && knobs().latent_mma != 0 && kv_rank <= 512 && cache_row % 8 == 0 && dp16 <= 704 &&
       (reinterpret_cast<uintptr_t>(cache) & 15u) == 0) {
     if (kv_rank <= 64) return launch_attn_mma<1>(a, st);
     if (kv_rank <= 128) return launch_attn_mma<2>(a, st);

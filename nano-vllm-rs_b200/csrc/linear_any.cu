@@ -125,6 +125,30 @@ __global__ void glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ ga
   }
 }
 
+
+// 8 bf16 values <-> one 16-byte vector
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+__global__ void glu_clamped_vec8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gate_up, int64_t n, int ff8, float limit) {
+  const int64_t total = n * ff8;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / ff8, c = i - r * ff8;
+    float g[8], u[8], o[8];
+    unpack8(reinterpret_cast<const uint4*>(gate_up)[r * 2 * ff8 + c], g);
+    unpack8(reinterpret_cast<const uint4*>(gate_up)[r * 2 * ff8 + ff8 + c], u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = glu_clamped(g[j], u[j], limit);
+    reinterpret_cast<uint4*>(out)[i] = pack8(o);
+  }
+}
+
 template <bool GLU>
 int launch_tile(const LinArgs& a, int m_tiles, int batch, int dtype, int out_dtype, cudaStream_t st) {
   dim3 grid((a.N + BN - 1) / BN, m_tiles, batch);
@@ -185,7 +209,11 @@ extern "C" int nvllm_glu_clamped(void* out, const void* gate_up, int32_t n, int3
   int64_t blocks = (total + 255) / 256;
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == NVLLM_BF16)
+  if (dtype == NVLLM_BF16 && ff % 8 == 0 && aligned16(out) && aligned16(gate_up)) {
+    int64_t b8 = (total / 8 + 255) / 256;
+    if (b8 > sm_count() * 16) b8 = sm_count() * 16;
+    glu_clamped_vec8_kernel<<<static_cast<unsigned>(b8), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(gate_up), n, ff / 8, limit);
+  } else if (dtype == NVLLM_BF16)
     glu_clamped_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(gate_up), n, ff, limit);
   else if (dtype == NVLLM_F32)
     glu_clamped_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), n, ff, limit);

@@ -130,6 +130,41 @@ __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ ex
   }
 }
 
+
+// 8 bf16 values <-> one 16-byte vector
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+}
+
+__global__ void moe_combine_vec8_kernel(bf16* __restrict__ out, const bf16* __restrict__ expert_out, const bf16* __restrict__ x,
+                                        const bf16* __restrict__ shared_out, const float* __restrict__ wts,
+                                        const int32_t* __restrict__ slot_row, int n, int hidden8, int top) {
+  const int64_t total = static_cast<int64_t>(n) * hidden8;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / hidden8, c = i - t * hidden8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, v[8];
+    for (int k = 0; k < top; ++k) {
+      const int64_t a = t * top + k;
+      const int r = slot_row[a];
+      unpack8(r >= 0 ? reinterpret_cast<const uint4*>(expert_out)[static_cast<int64_t>(r) * hidden8 + c] : reinterpret_cast<const uint4*>(x)[i], v);
+      const float w = wts[a];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(w, v[j], acc[j]);
+    }
+    if (shared_out) {
+      unpack8(reinterpret_cast<const uint4*>(shared_out)[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+    reinterpret_cast<uint4*>(out)[i] = pack8(acc);
+  }
+}
+
 }  // namespace
 }  // namespace nvllm
 
@@ -178,7 +213,13 @@ extern "C" int nvllm_moe_combine(void* out, const void* expert_out, const void* 
   int64_t blocks = (total + 255) / 256;
   if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == NVLLM_BF16)
+  if (dtype == NVLLM_BF16 && hidden % 8 == 0 && aligned16(out) && aligned16(expert_out) && aligned16(x) && aligned16(shared_out)) {
+    int64_t b8 = (total / 8 + 255) / 256;
+    if (b8 > sm_count() * 16) b8 = sm_count() * 16;
+    moe_combine_vec8_kernel<<<static_cast<unsigned>(b8), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(expert_out),
+                                                                      static_cast<const bf16*>(x), static_cast<const bf16*>(shared_out),
+                                                                      topk_w, slot_row, n, hidden / 8, top);
+  } else if (dtype == NVLLM_BF16)
     moe_combine_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(
         static_cast<bf16*>(out), static_cast<const bf16*>(expert_out), static_cast<const bf16*>(x),
         static_cast<const bf16*>(shared_out), topk_idx, topk_w, slot_row, n, hidden, top, experts);

@@ -82,6 +82,7 @@ ENGINE_PROTOTYPES = {
     "nvllm_runner_stream": (vp, [vp]),
     "nvllm_runner_profile": (i32, [vp, i32]),
     "nvllm_runner_profile_report": (i64, [vp, C.c_char_p, C.c_size_t]),
+    "nvllm_runner_set_eager": (i32, [vp, i32]),
     "nvllm_runner_last_launches": (i64, [vp]),
     "nvllm_runner_kv_cache": (i32, [vp, i32, C.POINTER(vp), C.POINTER(vp), C.POINTER(_ffi.KvLayout)]),
     "nvllm_runner_time_decode_attention": (i32, [vp, i32, C.POINTER(f32), C.POINTER(i64)]),
@@ -414,6 +415,10 @@ class ModelRunner:
             name, calls, us = line.split("\t")
             out[name] = (int(calls), float(us))
         return out
+
+    def set_eager(self, eager=True):
+        """Decode steps that follow run eagerly (True) or as CUDA graphs again (False)."""
+        check(lib().nvllm_runner_set_eager(self.h, int(eager)))
 
     def last_launches(self):
         return lib().nvllm_runner_last_launches(self.h)

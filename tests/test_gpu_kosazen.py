@@ -168,8 +168,9 @@ def test_latent_attention_paged_positions(cuda, dtype):
             np.testing.assert_allclose(got[i, h], ref, rtol=2e-2 if dtype == torch.bfloat16 else 1e-4, atol=2e-2 if dtype == torch.bfloat16 else 1e-5)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("where", ["first", "far", "page_end", "page_start", "last", "next"])
-def test_latent_attention_one_key_stands_out(cuda, where):
+def test_latent_attention_one_key_stands_out(cuda, where, dtype):
     """One cached row is made to dominate the scores: the output must be that row's latent when it is visible (the first
     token, a key hundreds back, a page's last / first slot, the query's own row) and must not show it when it lies one
     position in the future."""
@@ -179,24 +180,25 @@ def test_latent_attention_one_key_stands_out(cuda, where):
     ctx, qpos = 420, 400
     target = {"first": 0, "far": 37, "page_end": 16 * 20 - 1, "page_start": 16 * 20, "last": qpos, "next": qpos + 1}[where]
     cache, tables, seqs = _paged_case(rng, [ctx], bs, r + rd)
-    rows = seqs[0] * 0.05
+    rows = K.bf16_round(seqs[0] * 0.05)
     rows[target, r:] = 6.0                       # its rotated key part lines up with the query's
     blk, off = tables[0, target // bs], target % bs
     for j in range(ctx):
         cache[tables[0, j // bs] * bs + j % bs] = rows[j]
     q = np.zeros((1, H, dim + rd)); q[0, :, dim:] = 6.0
     q_abs = np.zeros((1, H * r))
-    out = ops.latent_attention(dev_t(q_abs, cuda, torch.float32), dev_t(q.reshape(1, -1), cuda, torch.float32),
+    out = ops.latent_attention(dev_t(q_abs, cuda, torch.float32), dev_t(q.reshape(1, -1), cuda, dtype),
                                torch.zeros(1, dtype=torch.int32, device=cuda), torch.tensor([qpos], dtype=torch.int64, device=cuda),
-                               torch.from_numpy(tables).to(cuda), bs, dev_t(cache, cuda, torch.float32), H, dim, rd, r, scale)
-    got = out.cpu().numpy().reshape(H, r)
+                               torch.from_numpy(tables).to(cuda), bs, dev_t(cache, cuda, dtype), H, dim, rd, r, scale)
+    got = out.float().cpu().numpy().reshape(H, r)
+    tol = 1e-5 if dtype == torch.float32 else 2e-3
     assert cache[blk * bs + off, r] == 6.0
     if where == "next":
         ref, _ = _attention_ref(np.zeros(r), q[0, 0, dim:], list(rows[:qpos + 1]), scale, r)
-        np.testing.assert_allclose(got[0], ref, rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(got[0], ref, rtol=1e-4, atol=tol)
         assert np.abs(got[0] - rows[target, :r]).max() > 0.01
     else:
-        np.testing.assert_allclose(got[0], rows[target, :r], atol=1e-5)   # exp(-(144 - small)) leaves nothing of the others
+        np.testing.assert_allclose(got[0], rows[target, :r], atol=tol)   # exp(-(144 - small)) leaves nothing of the others
 
 
 def test_moe_route_sort_grouped_combine(cuda):
