@@ -183,22 +183,25 @@ int launch_attn(const AttnArgs& a, cudaStream_t st) {
 
 // ---- tensor-core variant (bf16 operands) -------------------------------------------------------------------------------
 // With the key map folded into the query, all heads of a token score against the SAME cache rows: the heads are the M
-// dimension of the matrix products.  CTA = one query token x 16 heads, 4 warps, key tiles of 64 cache rows staged in shared
-// memory (bf16, rows padded against bank conflicts):
-//   S[16 x 64]  = Q[16 x (kv_rank + rot_dim)] . K^T      each warp 16 keys, mma.sync m16n8k16, f32 accumulate
+// dimension of the matrix products.  CTA = one query token x 16 heads, key tiles of 64 cache rows staged in shared
+// memory (bf16, rows padded against bank conflicts, double-buffered with cp.async):
+//   S[16 x 64]  = Q[16 x (kv_rank + rot_dim)] . K^T      mma.sync m16n8k16, f32 accumulate
 //   online softmax in f32 through shared memory (row max / sum / rescale factor), P rounded to bf16
-//   O[16 x kv_rank] += P[16 x 64] . C[64 x kv_rank]      each warp a quarter of the columns, C read with ldmatrix.trans
+//   O[16 x kv_rank] += P[16 x 64] . C[64 x kv_rank]      each warp its share of the columns, C read with ldmatrix.trans
 // Decoding is bound by reading the cache once per token; prompt portions re-read the tile per token from L2.
-constexpr int kMmaKeys = 64, kPsStride = 72, kSsStride = 68;
+constexpr int kMmaKeys = 64, kPsStride = 72, kSsStride = 68, kMmaThreads = 256;
 
-template <int NT2>  // the warp owns NT2 * 16 output columns; kv_rank padded to NT2 * 64
-__global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, int DPS, int DP16) {
+// 8 warps.  Scores: warp w takes 16 keys (w & 3) and one half of the reduction dimension (w >> 2), with two accumulators
+// per 8-key block so that the dependent mma chains stay short; the halves meet in shared memory.  Output: every warp owns
+// NT2 * 16 of the (padded) kv_rank columns.
+template <int NT2>  // kv_rank padded to NT2 * 128
+__global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const AttnArgs a, int DPS, int DP16) {
   extern __shared__ __align__(16) uint8_t smraw[];
   bf16* Qs = reinterpret_cast<bf16*>(smraw);          // [16][DPS]
   bf16* Kbuf = Qs + 16 * DPS;                         // 2 x [64][DPS]: the next tile lands while this one is used
   bf16* Ps = Kbuf + 2 * kMmaKeys * DPS;               // [16][kPsStride]
-  float* Ss = reinterpret_cast<float*>(Ps + 16 * kPsStride);  // [16][kSsStride]
-  float* m_s = Ss + 16 * kSsStride;
+  float* Ss = reinterpret_cast<float*>(Ps + 16 * kPsStride);  // 2 x [16][kSsStride]: one per half of the reduction
+  float* m_s = Ss + 2 * 16 * kSsStride;
   float* l_s = m_s + 16;
   float* c_s = l_s + 16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
@@ -210,13 +213,13 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
   constexpr int RC = NT2 * 16;
   const int vec_per_row = static_cast<int>(a.cache_row / 8);   // cache rows are padded to 8 elements (zeros)
   // zero everything once (padding rows / columns stay zero)
-  for (int e = tid; e < (16 + 2 * kMmaKeys) * DPS / 8; e += 128) reinterpret_cast<uint4*>(Qs)[e] = make_uint4(0, 0, 0, 0);
+  for (int e = tid; e < (16 + 2 * kMmaKeys) * DPS / 8; e += kMmaThreads) reinterpret_cast<uint4*>(Qs)[e] = make_uint4(0, 0, 0, 0);
   if (tid < 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
   __syncthreads();
-  // two threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
+  // four threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
   // the sequence's keys and for missing blocks)
   auto prefetch = [&](int j0, bf16* Ks) {
-    const int jj = tid >> 1, j = j0 + jj;
+    const int jj = tid >> 2, j = j0 + jj;
     const bf16* src = static_cast<const bf16*>(a.cache);
     int bytes = 0;
     if (j < nkeys) {
@@ -224,12 +227,12 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
       if (blk >= 0) { src += (static_cast<int64_t>(blk) * a.block_size + j % a.block_size) * a.cache_row; bytes = 16; }
     }
     const uint32_t dst = smem_u32(Ks + jj * DPS);
-    for (int v = tid & 1; v < vec_per_row; v += 2) cp_async_16(dst + v * 16, src + (bytes ? v * 8 : 0), bytes);
+    for (int v = tid & 3; v < vec_per_row; v += 4) cp_async_16(dst + v * 16, src + (bytes ? v * 8 : 0), bytes);
     cp_async_commit();
   };
   prefetch(0, Kbuf);
   // the queries: [folded q (f32 -> bf16) | rotated part]
-  for (int e = tid; e < 16 * D; e += 128) {
+  for (int e = tid; e < 16 * D; e += kMmaThreads) {
     const int r = e / D, d = e - r * D, h = hbase + r;
     if (h >= a.heads) continue;
     float v;
@@ -240,6 +243,8 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
   float acc[2 * NT2][4];
 #pragma unroll
   for (int i = 0; i < 2 * NT2; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const int nks = DP16 / 16, ks_mid = (nks + 1) / 2;
+  const int ks0 = (warp >> 2) ? ks_mid : 0, ks1 = (warp >> 2) ? nks : ks_mid;
   int buf = 0;
   for (int j0 = 0; j0 < nkeys; j0 += kMmaKeys, buf ^= 1) {
     bf16* Ks = Kbuf + buf * kMmaKeys * DPS;
@@ -250,37 +255,53 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
       cp_async_wait<0>();
     }
     __syncthreads();   // this tile (and, first time round, the queries) visible to all warps
-    {  // scores of this warp's 16 keys
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      const int krow = 16 * warp;
+    {  // partial scores: 16 keys x this warp's half of the reduction dimension
+      float s[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      const int krow = 16 * (warp & 3);
       const uint32_t qa = smem_u32(Qs + (lane & 15) * DPS + (lane >> 4) * 8);
       const uint32_t ka = smem_u32(Ks + (krow + (lane & 7) + 8 * (lane >> 4)) * DPS + 8 * ((lane >> 3) & 1));
-#pragma unroll 4
-      for (int ks = 0; ks < DP16 / 16; ++ks) {
+      int ks = ks0;
+      for (; ks + 1 < ks1; ks += 2) {
+        uint32_t af[4], bq[4], af2[4], bq2[4];
+        ldmatrix_x4(af, qa + ks * 32);
+        ldmatrix_x4(bq, ka + ks * 32);
+        ldmatrix_x4(af2, qa + ks * 32 + 32);
+        ldmatrix_x4(bq2, ka + ks * 32 + 32);
+        mma_bf16_16816(s[0], af, bq[0], bq[1]);
+        mma_bf16_16816(s[1], af, bq[2], bq[3]);
+        mma_bf16_16816(s[2], af2, bq2[0], bq2[1]);
+        mma_bf16_16816(s[3], af2, bq2[2], bq2[3]);
+      }
+      if (ks < ks1) {
         uint32_t af[4], bq[4];
         ldmatrix_x4(af, qa + ks * 32);
         ldmatrix_x4(bq, ka + ks * 32);
         mma_bf16_16816(s[0], af, bq[0], bq[1]);
         mma_bf16_16816(s[1], af, bq[2], bq[3]);
       }
+      float* So = Ss + (warp >> 2) * 16 * kSsStride;
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const int col = krow + nt * 8 + 2 * t4;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int j = j0 + col + c;
-          const bool ok = j < nkeys && table[j / a.block_size] >= 0;
-          Ss[g * kSsStride + col + c] = ok ? s[nt][c] * a.scale : -INFINITY;
-          Ss[(g + 8) * kSsStride + col + c] = ok ? s[nt][2 + c] * a.scale : -INFINITY;
-        }
+        So[g * kSsStride + col] = s[nt][0] + s[nt + 2][0];
+        So[g * kSsStride + col + 1] = s[nt][1] + s[nt + 2][1];
+        So[(g + 8) * kSsStride + col] = s[nt][2] + s[nt + 2][2];
+        So[(g + 8) * kSsStride + col + 1] = s[nt][3] + s[nt + 2][3];
       }
     }
     __syncthreads();
-    {  // online softmax: warp w owns rows 4w..4w+3, 8 lanes per row, 8 keys per lane
+    if (warp < 4) {  // online softmax: warp w owns rows 4w..4w+3, 8 lanes per row, 8 keys per lane
       const int row = 4 * warp + (lane >> 3), sub = lane & 7;
       float sv[8], mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { sv[i] = Ss[row * kSsStride + sub * 8 + i]; mx = fmaxf(mx, sv[i]); }
+      for (int i = 0; i < 8; ++i) {
+        const int j = j0 + sub * 8 + i;
+        const bool ok = j < nkeys && table[j / a.block_size] >= 0;
+        sv[i] = ok ? (Ss[row * kSsStride + sub * 8 + i] + Ss[(16 + row) * kSsStride + sub * 8 + i]) * a.scale : -INFINITY;
+        mx = fmaxf(mx, sv[i]);
+      }
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float m_old = m_s[row], m_new = fmaxf(m_old, mx);
@@ -340,13 +361,12 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const AttnArgs a, 
 
 template <int NT2>
 int launch_attn_mma(const AttnArgs& a, cudaStream_t st) {
-  const int D = a.kv_rank + a.rot_dim, DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 64;
-  (void)D;
+  const int DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 128;
   const int DPS = (DP16 > RP ? DP16 : RP) + 8;
-  const size_t smem = static_cast<size_t>(16 + 2 * kMmaKeys) * DPS * 2 + 16 * kPsStride * 2 + (16 * kSsStride + 48) * 4;
+  const size_t smem = static_cast<size_t>(16 + 2 * kMmaKeys) * DPS * 2 + 16 * kPsStride * 2 + (2 * 16 * kSsStride + 48) * 4;
   NVLLM_SMEM_ATTR_ONCE((latent_attn_mma_kernel<NT2>), 220 * 1024);
   dim3 grid(a.n, (a.heads + 15) / 16);
-  latent_attn_mma_kernel<NT2><<<grid, 128, smem, st>>>(a, DPS, DP16);
+  latent_attn_mma_kernel<NT2><<<grid, kMmaThreads, smem, st>>>(a, DPS, DP16);
   NVLLM_LAUNCH_CHECK("latent_attn_mma_kernel");
   return 0;
 }
@@ -413,10 +433,10 @@ extern "C" int nvllm_latent_attention(void* out, int64_t ldo, const float* q_abs
   const int dp16 = (static_cast<int>(cache_row) + 15) / 16 * 16;
   if (dtype == NVLLM_BF16 && knobs().latent_mma != 0 && kv_rank <= 512 && cache_row % 8 == 0 && dp16 <= 704 &&
       (reinterpret_cast<uintptr_t>(cache) & 15u) == 0) {
-    if (kv_rank <= 64) return launch_attn_mma<1>(a, st);
-    if (kv_rank <= 128) return launch_attn_mma<2>(a, st);
-    if (kv_rank <= 256) return launch_attn_mma<4>(a, st);
-    return launch_attn_mma<8>(a, st);
+    if (kv_rank <= 128) return launch_attn_mma<1>(a, st);
+    if (kv_rank <= 256) return launch_attn_mma<2>(a, st);
+    if (kv_rank <= 384) return launch_attn_mma<3>(a, st);
+    return launch_attn_mma<4>(a, st);
   }
   return dtype == NVLLM_BF16 ? dispatch_attn<bf16>(a, st) : dispatch_attn<float>(a, st);
 }
