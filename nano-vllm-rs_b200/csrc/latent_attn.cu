@@ -209,13 +209,16 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
   const int seq = a.tok_seq[t];
   const int nkeys = static_cast<int>(a.positions[t]) + 1;
   const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
-  const int D = a.kv_rank + a.rot_dim;
   constexpr int RC = NT2 * 16;
   const int vec_per_row = static_cast<int>(a.cache_row / 8);   // cache rows are padded to 8 elements (zeros)
-  // zero everything once (padding rows / columns stay zero)
-  for (int e = tid; e < (16 + 2 * kMmaKeys) * DPS / 8; e += kMmaThreads) reinterpret_cast<uint4*>(Qs)[e] = make_uint4(0, 0, 0, 0);
+  // zero once what no copy ever writes: the columns behind a cache row in every buffer row, and query rows of absent heads
+  {
+    const int pad0 = vec_per_row * 8, padw = DPS - pad0;   // DPS - cache_row columns (>= 8)
+    for (int e = tid; e < (16 + 2 * kMmaKeys) * padw; e += kMmaThreads) Qs[(e / padw) * DPS + pad0 + e % padw] = __float2bfloat16_rn(0.f);
+    const int absent0 = a.heads - hbase < 16 ? a.heads - hbase : 16;
+    for (int e = tid; e < (16 - absent0) * pad0; e += kMmaThreads) Qs[(absent0 + e / pad0) * DPS + e % pad0] = __float2bfloat16_rn(0.f);
+  }
   if (tid < 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
-  __syncthreads();
   // four threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
   // the sequence's keys and for missing blocks)
   auto prefetch = [&](int j0, bf16* Ks) {
@@ -231,14 +234,29 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
     cp_async_commit();
   };
   prefetch(0, Kbuf);
-  // the queries: [folded q (f32 -> bf16) | rotated part]
-  for (int e = tid; e < 16 * D; e += kMmaThreads) {
-    const int r = e / D, d = e - r * D, h = hbase + r;
-    if (h >= a.heads) continue;
-    float v;
-    if (d < a.kv_rank) v = a.q_abs[static_cast<int64_t>(t) * a.ldqa + static_cast<int64_t>(h) * a.kv_rank + d];
-    else v = __bfloat162float(static_cast<const bf16*>(a.q)[static_cast<int64_t>(t) * a.ldq + static_cast<int64_t>(h) * (a.dim + a.rot_dim) + a.dim + (d - a.kv_rank)]);
-    Qs[r * DPS + d] = __float2bfloat16_rn(v);
+  // the queries: [folded q (f32 -> bf16) | rotated part | zeros up to the cache row's width]
+  {
+    const int heads_here = a.heads - hbase < 16 ? a.heads - hbase : 16, pad0 = vec_per_row * 8;
+    const float* qa = a.q_abs + static_cast<int64_t>(t) * a.ldqa + static_cast<int64_t>(hbase) * a.kv_rank;
+    const bf16* qr = static_cast<const bf16*>(a.q) + static_cast<int64_t>(t) * a.ldq + static_cast<int64_t>(hbase) * (a.dim + a.rot_dim) + a.dim;
+    if (a.kv_rank % 4 == 0 && (reinterpret_cast<uintptr_t>(qa) & 15u) == 0) {   // rows of one token are contiguous: 16-byte loads
+      const int q4 = a.kv_rank / 4;
+      for (int e = tid; e < heads_here * q4; e += kMmaThreads) {
+        const int r = e / q4, c = (e - r * q4) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(qa + static_cast<int64_t>(r) * a.kv_rank + c);
+        *reinterpret_cast<uint2*>(Qs + r * DPS + c) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+      }
+    } else {
+      for (int e = tid; e < heads_here * a.kv_rank; e += kMmaThreads) {
+        const int r = e / a.kv_rank, c = e - r * a.kv_rank;
+        Qs[r * DPS + c] = __float2bfloat16_rn(qa[static_cast<int64_t>(r) * a.kv_rank + c]);
+      }
+    }
+    const int tail = pad0 - a.kv_rank;   // rotated part, then zeros
+    for (int e = tid; e < heads_here * tail; e += kMmaThreads) {
+      const int r = e / tail, c = e - r * tail;
+      Qs[r * DPS + a.kv_rank + c] = c < a.rot_dim ? qr[static_cast<int64_t>(r) * (a.dim + a.rot_dim) + c] : __float2bfloat16_rn(0.f);
+    }
   }
   float acc[2 * NT2][4];
 #pragma unroll
