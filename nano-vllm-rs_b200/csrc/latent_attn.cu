@@ -207,8 +207,10 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   const int t = blockIdx.x, hbase = blockIdx.y * 16;
   const int seq = a.tok_seq[t];
-  const int nkeys = static_cast<int>(a.positions[t]) + 1;
   const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
+  int nkeys = static_cast<int>(a.positions[t]) + 1;
+  for (int b = 0; b * a.block_size < nkeys; ++b)   // a missing block ends the sequence's keys (padding rows of a graph: none)
+    if (table[b] < 0) { nkeys = b * a.block_size; break; }
   constexpr int RC = NT2 * 16;
   const int vec_per_row = static_cast<int>(a.cache_row / 8);   // cache rows are padded to 8 elements (zeros)
   // zero once what no copy ever writes: the columns behind a cache row in every buffer row, and query rows of absent heads
@@ -315,8 +317,7 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
       float sv[8], mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int j = j0 + sub * 8 + i;
-        const bool ok = j < nkeys && table[j / a.block_size] >= 0;
+        const bool ok = j0 + sub * 8 + i < nkeys;
         sv[i] = ok ? (Ss[row * kSsStride + sub * 8 + i] + Ss[(16 + row) * kSsStride + sub * 8 + i]) * a.scale : -INFINITY;
         mx = fmaxf(mx, sv[i]);
       }
@@ -344,16 +345,19 @@ __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const Attn
     __syncthreads();
     {  // O += P . C over this warp's RC columns
       const float cg = c_s[g], cg8 = c_s[g + 8];
+      const uint32_t pa = smem_u32(Ps + (lane & 15) * kPsStride + (lane >> 4) * 8);
+      const uint32_t va = smem_u32(Ks + ((lane & 7) + 8 * ((lane >> 3) & 1)) * DPS + warp * RC + 8 * (lane >> 4));
+      const uint32_t vstep = static_cast<uint32_t>(DPS) * 32;   // 16 cache rows in bytes
 #pragma unroll
       for (int i = 0; i < 2 * NT2; ++i) { acc[i][0] *= cg; acc[i][1] *= cg; acc[i][2] *= cg8; acc[i][3] *= cg8; }
 #pragma unroll
       for (int kk = 0; kk < kMmaKeys / 16; ++kk) {
         uint32_t pf[4];
-        ldmatrix_x4(pf, smem_u32(Ps + (lane & 15) * kPsStride + kk * 16 + (lane >> 4) * 8));
+        ldmatrix_x4(pf, pa + kk * 32);
 #pragma unroll
         for (int p2 = 0; p2 < NT2; ++p2) {
           uint32_t bv[4];
-          ldmatrix_x4_trans(bv, smem_u32(Ks + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DPS + warp * RC + p2 * 16 + 8 * (lane >> 4)));
+          ldmatrix_x4_trans(bv, va + kk * vstep + p2 * 32);
           mma_bf16_16816(acc[2 * p2], pf, bv[0], bv[1]);
           mma_bf16_16816(acc[2 * p2 + 1], pf, bv[2], bv[3]);
         }
