@@ -486,3 +486,37 @@ def test_grouped_tensor_core_gemm(cuda):
             if e < E:
                 assert te[sr[t, k] // 128] == e
                 np.testing.assert_allclose(y[sr[t, k]], x[t] @ w[e].T, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_latent_attention_whole_prompts_in_one_launch(cuda, dtype):
+    """Every position of several sequences as a query in ONE launch (whole prompts side by side): odd and even lengths,
+    a one-token sequence, sequences that end inside and exactly on a page."""
+    from nano_vllm_rs_b200 import ops
+    rng = np.random.default_rng(16)
+    H, dim, rd, r, bs, scale = 3, 8, 6, 40, 16, 0.3
+    ctx = [5, 130, 131, 64, 1, 77]
+    cache, tables, seqs = _paged_case(rng, ctx, bs, r + rd)
+    if dtype == torch.bfloat16:
+        cache, seqs = K.bf16_round(cache), [K.bf16_round(s) for s in seqs]
+    tok_seq = np.concatenate([np.full(c, b) for b, c in enumerate(ctx)]).astype(np.int32)
+    pos = np.concatenate([np.arange(c) for c in ctx]).astype(np.int64)
+    n = len(pos)
+    q_abs = rng.standard_normal((n, H, r)).astype(np.float32)
+    q = K.bf16_round(rng.standard_normal((n, H, dim + rd)))
+    out = ops.latent_attention(dev_t(q_abs.reshape(n, -1), cuda, torch.float32), dev_t(q.reshape(n, -1), cuda, dtype),
+                               torch.from_numpy(tok_seq).to(cuda), torch.from_numpy(pos).to(cuda), torch.from_numpy(tables).to(cuda),
+                               bs, dev_t(cache, cuda, dtype), H, dim, rd, r, scale)
+    got = out.float().cpu().numpy().reshape(n, H, r)
+    qa = K.bf16_round(q_abs) if dtype == torch.bfloat16 else q_abs.astype(np.float64)   # the bf16 kernel rounds the folded query
+    t0 = 0
+    for b, c in enumerate(ctx):
+        rows = seqs[b]
+        for h in range(H):
+            s = (qa[t0:t0 + c, h] @ rows[:, :r].T + q[t0:t0 + c, h, dim:] @ rows[:, r:].T) * scale
+            s = np.where(np.tril(np.ones((c, c), bool)), s, -np.inf)
+            p = np.exp(s - s.max(-1, keepdims=True))
+            ref = (p / p.sum(-1, keepdims=True)) @ rows[:, :r]
+            np.testing.assert_allclose(got[t0:t0 + c, h], ref, rtol=2e-2 if dtype == torch.bfloat16 else 1e-4,
+                                       atol=2e-2 if dtype == torch.bfloat16 else 1e-5)
+        t0 += c
