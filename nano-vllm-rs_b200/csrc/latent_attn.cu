@@ -193,204 +193,271 @@ constexpr int kMmaKeys = 64, kPsStride = 72, kSsStride = 68, kMmaThreads = 256;
 
 // 8 warps.  Scores: warp w takes 16 keys (w & 3) and one half of the reduction dimension (w >> 2), with two accumulators
 // per 8-key block so that the dependent mma chains stay short; the halves meet in shared memory.  Output: every warp owns
-// NT2 * 16 of the (padded) kv_rank columns.
-template <int NT2>  // kv_rank padded to NT2 * 128
+// NT2 * 16 of the (padded) kv_rank columns.  TQ = 2 (large batches, i.e. prompt portions): the CTA takes two consecutive
+// tokens of the batch; when they belong to the same sequence they share every key tile and every B fragment (the kernel is
+// bound by instruction issue and latency, not by the tensor pipe, so the second token is almost free); when they do not,
+// the CTA runs them one after the other.
+template <int NT2, int TQ>  // kv_rank padded to NT2 * 128
 __global__ void __launch_bounds__(kMmaThreads) latent_attn_mma_kernel(const AttnArgs a, int DPS, int DP16) {
   extern __shared__ __align__(16) uint8_t smraw[];
-  bf16* Qs = reinterpret_cast<bf16*>(smraw);          // [16][DPS]
-  bf16* Kbuf = Qs + 16 * DPS;                         // 2 x [64][DPS]: the next tile lands while this one is used
-  bf16* Ps = Kbuf + 2 * kMmaKeys * DPS;               // [16][kPsStride]
-  float* Ss = reinterpret_cast<float*>(Ps + 16 * kPsStride);  // 2 x [16][kSsStride]: one per half of the reduction
-  float* m_s = Ss + 2 * 16 * kSsStride;
-  float* l_s = m_s + 16;
-  float* c_s = l_s + 16;
+  bf16* Qs = reinterpret_cast<bf16*>(smraw);          // TQ x [16][DPS]
+  bf16* Kbuf = Qs + TQ * 16 * DPS;                    // 2 x [64][DPS]: the next tile lands while this one is used
+  bf16* Ps = Kbuf + 2 * kMmaKeys * DPS;               // TQ x [16][kPsStride]
+  float* Ss = reinterpret_cast<float*>(Ps + TQ * 16 * kPsStride);  // TQ x 2 x [16][kSsStride]: one per half of the reduction
+  float* m_s = Ss + TQ * 2 * 16 * kSsStride;          // TQ x 16 each
+  float* l_s = m_s + TQ * 16;
+  float* c_s = l_s + TQ * 16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-  const int t = blockIdx.x, hbase = blockIdx.y * 16;
-  const int seq = a.tok_seq[t];
-  const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
-  int nkeys = static_cast<int>(a.positions[t]) + 1;
-  for (int b = 0; b * a.block_size < nkeys; ++b)   // a missing block ends the sequence's keys (padding rows of a graph: none)
-    if (table[b] < 0) { nkeys = b * a.block_size; break; }
+  const int hbase = blockIdx.y * 16;
   constexpr int RC = NT2 * 16;
   const int vec_per_row = static_cast<int>(a.cache_row / 8);   // cache rows are padded to 8 elements (zeros)
-  // zero once what no copy ever writes: the columns behind a cache row in every buffer row, and query rows of absent heads
-  {
-    const int pad0 = vec_per_row * 8, padw = DPS - pad0;   // DPS - cache_row columns (>= 8)
-    for (int e = tid; e < (16 + 2 * kMmaKeys) * padw; e += kMmaThreads) Qs[(e / padw) * DPS + pad0 + e % padw] = __float2bfloat16_rn(0.f);
-    const int absent0 = a.heads - hbase < 16 ? a.heads - hbase : 16;
-    for (int e = tid; e < (16 - absent0) * pad0; e += kMmaThreads) Qs[(absent0 + e / pad0) * DPS + e % pad0] = __float2bfloat16_rn(0.f);
-  }
-  if (tid < 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
-  // four threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
-  // the sequence's keys and for missing blocks)
-  auto prefetch = [&](int j0, bf16* Ks) {
-    const int jj = tid >> 2, j = j0 + jj;
-    const bf16* src = static_cast<const bf16*>(a.cache);
-    int bytes = 0;
-    if (j < nkeys) {
-      const int32_t blk = table[j / a.block_size];
-      if (blk >= 0) { src += (static_cast<int64_t>(blk) * a.block_size + j % a.block_size) * a.cache_row; bytes = 16; }
-    }
-    const uint32_t dst = smem_u32(Ks + jj * DPS);
-    for (int v = tid & 3; v < vec_per_row; v += 4) cp_async_16(dst + v * 16, src + (bytes ? v * 8 : 0), bytes);
-    cp_async_commit();
-  };
-  prefetch(0, Kbuf);
-  // the queries: [folded q (f32 -> bf16) | rotated part | zeros up to the cache row's width]
-  {
-    const int heads_here = a.heads - hbase < 16 ? a.heads - hbase : 16, pad0 = vec_per_row * 8;
-    const float* qa = a.q_abs + static_cast<int64_t>(t) * a.ldqa + static_cast<int64_t>(hbase) * a.kv_rank;
-    const bf16* qr = static_cast<const bf16*>(a.q) + static_cast<int64_t>(t) * a.ldq + static_cast<int64_t>(hbase) * (a.dim + a.rot_dim) + a.dim;
-    if (a.kv_rank % 4 == 0 && (reinterpret_cast<uintptr_t>(qa) & 15u) == 0) {   // rows of one token are contiguous: 16-byte loads
-      const int q4 = a.kv_rank / 4;
-      for (int e = tid; e < heads_here * q4; e += kMmaThreads) {
-        const int r = e / q4, c = (e - r * q4) * 4;
-        const float4 v = *reinterpret_cast<const float4*>(qa + static_cast<int64_t>(r) * a.kv_rank + c);
-        *reinterpret_cast<uint2*>(Qs + r * DPS + c) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
-      }
-    } else {
-      for (int e = tid; e < heads_here * a.kv_rank; e += kMmaThreads) {
-        const int r = e / a.kv_rank, c = e - r * a.kv_rank;
-        Qs[r * DPS + c] = __float2bfloat16_rn(qa[static_cast<int64_t>(r) * a.kv_rank + c]);
-      }
-    }
-    const int tail = pad0 - a.kv_rank;   // rotated part, then zeros
-    for (int e = tid; e < heads_here * tail; e += kMmaThreads) {
-      const int r = e / tail, c = e - r * tail;
-      Qs[r * DPS + a.kv_rank + c] = c < a.rot_dim ? qr[static_cast<int64_t>(r) * (a.dim + a.rot_dim) + c] : __float2bfloat16_rn(0.f);
-    }
-  }
-  float acc[2 * NT2][4];
-#pragma unroll
-  for (int i = 0; i < 2 * NT2; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const int pad0 = vec_per_row * 8, heads_here = a.heads - hbase < 16 ? a.heads - hbase : 16;
   const int nks = DP16 / 16, ks_mid = (nks + 1) / 2;
   const int ks0 = (warp >> 2) ? ks_mid : 0, ks1 = (warp >> 2) ? nks : ks_mid;
-  int buf = 0;
-  for (int j0 = 0; j0 < nkeys; j0 += kMmaKeys, buf ^= 1) {
-    bf16* Ks = Kbuf + buf * kMmaKeys * DPS;
-    if (j0 + kMmaKeys < nkeys) {
-      prefetch(j0 + kMmaKeys, Kbuf + (buf ^ 1) * kMmaKeys * DPS);   // that buffer's last readers passed the barrier below
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+  // zero once what no copy ever writes: the columns behind a cache row in every buffer row, and query rows of absent heads
+  {
+    const int padw = DPS - pad0;   // >= 8
+    for (int e = tid; e < (TQ * 16 + 2 * kMmaKeys) * padw; e += kMmaThreads) Qs[(e / padw) * DPS + pad0 + e % padw] = __float2bfloat16_rn(0.f);
+    for (int q = 0; q < TQ; ++q)
+      for (int e = tid; e < (16 - heads_here) * pad0; e += kMmaThreads)
+        Qs[(q * 16 + heads_here + e / pad0) * DPS + e % pad0] = __float2bfloat16_rn(0.f);
+  }
+  const int tfirst = blockIdx.x * TQ;
+  bool together = false;
+  if (TQ == 2 && tfirst + 1 < a.n) together = a.tok_seq[tfirst] == a.tok_seq[tfirst + 1];
+  const int npass = (TQ == 1 || together || tfirst + 1 >= a.n) ? 1 : 2;
+  for (int pass = 0; pass < npass; ++pass) {
+    // tokens of this pass: slot q holds token tq[q] (-1: slot unused)
+    int tq[TQ], nk[TQ], nkeys = 0;
+    const int t_lead = tfirst + pass;
+    const int32_t* table = a.tables + static_cast<int64_t>(a.tok_seq[t_lead]) * a.table_cap;
+#pragma unroll
+    for (int q = 0; q < TQ; ++q) {
+      tq[q] = (q == 0) ? t_lead : (together ? tfirst + 1 : -1);
+      nk[q] = tq[q] >= 0 ? static_cast<int>(a.positions[tq[q]]) + 1 : 0;
+      nkeys = nk[q] > nkeys ? nk[q] : nkeys;
     }
-    __syncthreads();   // this tile (and, first time round, the queries) visible to all warps
-    {  // partial scores: 16 keys x this warp's half of the reduction dimension
-      float s[4][4];
+    for (int b = 0; b * a.block_size < nkeys; ++b)   // a missing block ends the sequence's keys (padding rows of a graph: none)
+      if (table[b] < 0) { nkeys = b * a.block_size; break; }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-      const int krow = 16 * (warp & 3);
-      const uint32_t qa = smem_u32(Qs + (lane & 15) * DPS + (lane >> 4) * 8);
-      const uint32_t ka = smem_u32(Ks + (krow + (lane & 7) + 8 * (lane >> 4)) * DPS + 8 * ((lane >> 3) & 1));
-      int ks = ks0;
-      for (; ks + 1 < ks1; ks += 2) {
-        uint32_t af[4], bq[4], af2[4], bq2[4];
-        ldmatrix_x4(af, qa + ks * 32);
-        ldmatrix_x4(bq, ka + ks * 32);
-        ldmatrix_x4(af2, qa + ks * 32 + 32);
-        ldmatrix_x4(bq2, ka + ks * 32 + 32);
-        mma_bf16_16816(s[0], af, bq[0], bq[1]);
-        mma_bf16_16816(s[1], af, bq[2], bq[3]);
-        mma_bf16_16816(s[2], af2, bq2[0], bq2[1]);
-        mma_bf16_16816(s[3], af2, bq2[2], bq2[3]);
+    for (int q = 0; q < TQ; ++q) nk[q] = nk[q] < nkeys ? nk[q] : nkeys;
+    __syncthreads();   // previous pass done with every buffer; the zero fill above is ordered before the copies below
+    if (tid < TQ * 16) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; c_s[tid] = 1.f; }
+    // four threads per cache row: one block-table look-up per thread and tile, 16-byte asynchronous copies (zero fill past
+    // the sequence's keys)
+    auto prefetch = [&](int j0, bf16* Ks) {
+      const int jj = tid >> 2, j = j0 + jj;
+      const bf16* src = static_cast<const bf16*>(a.cache);
+      int bytes = 0;
+      if (j < nkeys) {
+        src += (static_cast<int64_t>(table[j / a.block_size]) * a.block_size + j % a.block_size) * a.cache_row;
+        bytes = 16;
       }
-      if (ks < ks1) {
-        uint32_t af[4], bq[4];
-        ldmatrix_x4(af, qa + ks * 32);
-        ldmatrix_x4(bq, ka + ks * 32);
-        mma_bf16_16816(s[0], af, bq[0], bq[1]);
-        mma_bf16_16816(s[1], af, bq[2], bq[3]);
+      const uint32_t dst = smem_u32(Ks + jj * DPS);
+      for (int v = tid & 3; v < vec_per_row; v += 4) cp_async_16(dst + v * 16, src + (bytes ? v * 8 : 0), bytes);
+      cp_async_commit();
+    };
+    prefetch(0, Kbuf);
+    // the queries: [folded q (f32 -> bf16) | rotated part | zeros up to the cache row's width]
+#pragma unroll
+    for (int q = 0; q < TQ; ++q) {
+      bf16* Qq = Qs + q * 16 * DPS;
+      if (tq[q] < 0) {
+        for (int e = tid; e < heads_here * pad0; e += kMmaThreads) Qq[(e / pad0) * DPS + e % pad0] = __float2bfloat16_rn(0.f);
+        continue;
       }
-      float* So = Ss + (warp >> 2) * 16 * kSsStride;
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const int col = krow + nt * 8 + 2 * t4;
-        So[g * kSsStride + col] = s[nt][0] + s[nt + 2][0];
-        So[g * kSsStride + col + 1] = s[nt][1] + s[nt + 2][1];
-        So[(g + 8) * kSsStride + col] = s[nt][2] + s[nt + 2][2];
-        So[(g + 8) * kSsStride + col + 1] = s[nt][3] + s[nt + 2][3];
-      }
-    }
-    __syncthreads();
-    if (warp < 4) {  // online softmax: warp w owns rows 4w..4w+3, 8 lanes per row, 8 keys per lane
-      const int row = 4 * warp + (lane >> 3), sub = lane & 7;
-      float sv[8], mx = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const bool ok = j0 + sub * 8 + i < nkeys;
-        sv[i] = ok ? (Ss[row * kSsStride + sub * 8 + i] + Ss[(16 + row) * kSsStride + sub * 8 + i]) * a.scale : -INFINITY;
-        mx = fmaxf(mx, sv[i]);
-      }
-#pragma unroll
-      for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      const float m_old = m_s[row], m_new = fmaxf(m_old, mx);
-      float sum = 0.f, pv[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        pv[i] = (sv[i] == -INFINITY) ? 0.f : expf(sv[i] - m_new);
-        sum += pv[i];
-      }
-      *reinterpret_cast<uint4*>(Ps + row * kPsStride + sub * 8) =
-          make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]), pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
-#pragma unroll
-      for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      __syncwarp();
-      if (sub == 0) {
-        const float corr = (m_new == -INFINITY || m_old == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f) : expf(m_old - m_new);
-        c_s[row] = corr;
-        l_s[row] = l_s[row] * corr + sum;
-        m_s[row] = m_new;
-      }
-    }
-    __syncthreads();
-    {  // O += P . C over this warp's RC columns
-      const float cg = c_s[g], cg8 = c_s[g + 8];
-      const uint32_t pa = smem_u32(Ps + (lane & 15) * kPsStride + (lane >> 4) * 8);
-      const uint32_t va = smem_u32(Ks + ((lane & 7) + 8 * ((lane >> 3) & 1)) * DPS + warp * RC + 8 * (lane >> 4));
-      const uint32_t vstep = static_cast<uint32_t>(DPS) * 32;   // 16 cache rows in bytes
-#pragma unroll
-      for (int i = 0; i < 2 * NT2; ++i) { acc[i][0] *= cg; acc[i][1] *= cg; acc[i][2] *= cg8; acc[i][3] *= cg8; }
-#pragma unroll
-      for (int kk = 0; kk < kMmaKeys / 16; ++kk) {
-        uint32_t pf[4];
-        ldmatrix_x4(pf, pa + kk * 32);
-#pragma unroll
-        for (int p2 = 0; p2 < NT2; ++p2) {
-          uint32_t bv[4];
-          ldmatrix_x4_trans(bv, va + kk * vstep + p2 * 32);
-          mma_bf16_16816(acc[2 * p2], pf, bv[0], bv[1]);
-          mma_bf16_16816(acc[2 * p2 + 1], pf, bv[2], bv[3]);
+      const float* qa = a.q_abs + static_cast<int64_t>(tq[q]) * a.ldqa + static_cast<int64_t>(hbase) * a.kv_rank;
+      const bf16* qr = static_cast<const bf16*>(a.q) + static_cast<int64_t>(tq[q]) * a.ldq + static_cast<int64_t>(hbase) * (a.dim + a.rot_dim) + a.dim;
+      if (a.kv_rank % 4 == 0 && (reinterpret_cast<uintptr_t>(qa) & 15u) == 0) {   // rows of one token are contiguous: 16-byte loads
+        const int q4 = a.kv_rank / 4;
+        for (int e = tid; e < heads_here * q4; e += kMmaThreads) {
+          const int r = e / q4, c = (e - r * q4) * 4;
+          const float4 v = *reinterpret_cast<const float4*>(qa + static_cast<int64_t>(r) * a.kv_rank + c);
+          *reinterpret_cast<uint2*>(Qq + r * DPS + c) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+        }
+      } else {
+        for (int e = tid; e < heads_here * a.kv_rank; e += kMmaThreads) {
+          const int r = e / a.kv_rank, c = e - r * a.kv_rank;
+          Qq[r * DPS + c] = __float2bfloat16_rn(qa[static_cast<int64_t>(r) * a.kv_rank + c]);
         }
       }
-    }
-    __syncthreads();   // tile, P and the row factors are free again
-  }
-  bf16* out = static_cast<bf16*>(a.out) + static_cast<int64_t>(t) * a.ldo;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = g + 8 * half, h = hbase + r;
-    if (h >= a.heads) continue;
-    const float l = l_s[r], inv = l > 0.f ? 1.0f / l : 0.f;
-#pragma unroll
-    for (int nt = 0; nt < 2 * NT2; ++nt)
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int col = warp * RC + nt * 8 + 2 * t4 + c;
-        if (col < a.kv_rank) out[static_cast<int64_t>(h) * a.kv_rank + col] = __float2bfloat16_rn(acc[nt][2 * half + c] * inv);
+      const int tail = pad0 - a.kv_rank;   // rotated part, then zeros
+      for (int e = tid; e < heads_here * tail; e += kMmaThreads) {
+        const int r = e / tail, c = e - r * tail;
+        Qq[r * DPS + a.kv_rank + c] = c < a.rot_dim ? qr[static_cast<int64_t>(r) * (a.dim + a.rot_dim) + c] : __float2bfloat16_rn(0.f);
       }
+    }
+    float acc[TQ][2 * NT2][4];
+#pragma unroll
+    for (int q = 0; q < TQ; ++q)
+#pragma unroll
+      for (int i = 0; i < 2 * NT2; ++i) acc[q][i][0] = acc[q][i][1] = acc[q][i][2] = acc[q][i][3] = 0.f;
+    int buf = 0;
+    for (int j0 = 0; j0 < nkeys; j0 += kMmaKeys, buf ^= 1) {
+      bf16* Ks = Kbuf + buf * kMmaKeys * DPS;
+      if (j0 + kMmaKeys < nkeys) {
+        prefetch(j0 + kMmaKeys, Kbuf + (buf ^ 1) * kMmaKeys * DPS);   // that buffer's last readers passed the barrier below
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();   // this tile (and, first time round, the queries) visible to all warps
+      {  // partial scores: 16 keys x this warp's half of the reduction dimension, for every token of the CTA
+        float s[TQ][4][4];
+#pragma unroll
+        for (int q = 0; q < TQ; ++q)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s[q][i][0] = s[q][i][1] = s[q][i][2] = s[q][i][3] = 0.f;
+        const int krow = 16 * (warp & 3);
+        const uint32_t qa = smem_u32(Qs + (lane & 15) * DPS + (lane >> 4) * 8);
+        const uint32_t ka = smem_u32(Ks + (krow + (lane & 7) + 8 * (lane >> 4)) * DPS + 8 * ((lane >> 3) & 1));
+        const uint32_t qstep = static_cast<uint32_t>(DPS) * 32;   // 16 query rows in bytes
+        int ks = ks0;
+        for (; ks + 1 < ks1; ks += 2) {
+          uint32_t bq[4], bq2[4];
+          ldmatrix_x4(bq, ka + ks * 32);
+          ldmatrix_x4(bq2, ka + ks * 32 + 32);
+#pragma unroll
+          for (int q = 0; q < TQ; ++q) {
+            uint32_t af[4], af2[4];
+            ldmatrix_x4(af, qa + q * qstep + ks * 32);
+            ldmatrix_x4(af2, qa + q * qstep + ks * 32 + 32);
+            mma_bf16_16816(s[q][0], af, bq[0], bq[1]);
+            mma_bf16_16816(s[q][1], af, bq[2], bq[3]);
+            mma_bf16_16816(s[q][2], af2, bq2[0], bq2[1]);
+            mma_bf16_16816(s[q][3], af2, bq2[2], bq2[3]);
+          }
+        }
+        if (ks < ks1) {
+          uint32_t bq[4];
+          ldmatrix_x4(bq, ka + ks * 32);
+#pragma unroll
+          for (int q = 0; q < TQ; ++q) {
+            uint32_t af[4];
+            ldmatrix_x4(af, qa + q * qstep + ks * 32);
+            mma_bf16_16816(s[q][0], af, bq[0], bq[1]);
+            mma_bf16_16816(s[q][1], af, bq[2], bq[3]);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < TQ; ++q) {
+          float* So = Ss + (q * 2 + (warp >> 2)) * 16 * kSsStride;
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const int col = krow + nt * 8 + 2 * t4;
+            So[g * kSsStride + col] = s[q][nt][0] + s[q][nt + 2][0];
+            So[g * kSsStride + col + 1] = s[q][nt][1] + s[q][nt + 2][1];
+            So[(g + 8) * kSsStride + col] = s[q][nt][2] + s[q][nt + 2][2];
+            So[(g + 8) * kSsStride + col + 1] = s[q][nt][3] + s[q][nt + 2][3];
+          }
+        }
+      }
+      __syncthreads();
+      if (warp < 4 * TQ) {  // online softmax: warps 0-3 token 0, warps 4-7 token 1; 4 rows per warp, 8 lanes per row, 8 keys per lane
+        const int q = warp >> 2, row = 4 * (warp & 3) + (lane >> 3), sub = lane & 7;
+        const float* S0 = Ss + q * 2 * 16 * kSsStride;
+        const int nkq = (TQ == 1) ? nk[0] : (q == 0 ? nk[0] : nk[TQ - 1]);
+        float sv[8], mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const bool ok = j0 + sub * 8 + i < nkq;
+          sv[i] = ok ? (S0[row * kSsStride + sub * 8 + i] + S0[(16 + row) * kSsStride + sub * 8 + i]) * a.scale : -INFINITY;
+          mx = fmaxf(mx, sv[i]);
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_old = m_s[q * 16 + row], m_new = fmaxf(m_old, mx);
+        float sum = 0.f, pv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          pv[i] = (sv[i] == -INFINITY) ? 0.f : expf(sv[i] - m_new);
+          sum += pv[i];
+        }
+        *reinterpret_cast<uint4*>(Ps + (q * 16 + row) * kPsStride + sub * 8) =
+            make_uint4(pack_bf16x2(pv[0], pv[1]), pack_bf16x2(pv[2], pv[3]), pack_bf16x2(pv[4], pv[5]), pack_bf16x2(pv[6], pv[7]));
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        __syncwarp();
+        if (sub == 0) {
+          const float corr = (m_new == -INFINITY || m_old == -INFINITY) ? (m_new == -INFINITY ? 1.f : 0.f) : expf(m_old - m_new);
+          c_s[q * 16 + row] = corr;
+          l_s[q * 16 + row] = l_s[q * 16 + row] * corr + sum;
+          m_s[q * 16 + row] = m_new;
+        }
+      }
+      __syncthreads();
+      {  // O += P . C over this warp's RC columns
+#pragma unroll
+        for (int q = 0; q < TQ; ++q) {
+          const float cg = c_s[q * 16 + g], cg8 = c_s[q * 16 + g + 8];
+#pragma unroll
+          for (int i = 0; i < 2 * NT2; ++i) { acc[q][i][0] *= cg; acc[q][i][1] *= cg; acc[q][i][2] *= cg8; acc[q][i][3] *= cg8; }
+        }
+        const uint32_t pa = smem_u32(Ps + (lane & 15) * kPsStride + (lane >> 4) * 8);
+        const uint32_t va = smem_u32(Ks + ((lane & 7) + 8 * ((lane >> 3) & 1)) * DPS + warp * RC + 8 * (lane >> 4));
+        const uint32_t vstep = static_cast<uint32_t>(DPS) * 32;   // 16 cache rows in bytes
+#pragma unroll
+        for (int kk = 0; kk < kMmaKeys / 16; ++kk) {
+          uint32_t pf[TQ][4];
+#pragma unroll
+          for (int q = 0; q < TQ; ++q) ldmatrix_x4(pf[q], pa + q * (16 * kPsStride * 2) + kk * 32);
+#pragma unroll
+          for (int p2 = 0; p2 < NT2; ++p2) {
+            uint32_t bv[4];
+            ldmatrix_x4_trans(bv, va + kk * vstep + p2 * 32);
+#pragma unroll
+            for (int q = 0; q < TQ; ++q) {
+              mma_bf16_16816(acc[q][2 * p2], pf[q], bv[0], bv[1]);
+              mma_bf16_16816(acc[q][2 * p2 + 1], pf[q], bv[2], bv[3]);
+            }
+          }
+        }
+      }
+      __syncthreads();   // tile, P and the row factors are free again
+    }
+#pragma unroll
+    for (int q = 0; q < TQ; ++q) {
+      if (tq[q] < 0) continue;
+      bf16* out = static_cast<bf16*>(a.out) + static_cast<int64_t>(tq[q]) * a.ldo;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = g + 8 * half, h = hbase + r;
+        if (h >= a.heads) continue;
+        const float l = l_s[q * 16 + r], inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2 * NT2; ++nt)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int col = warp * RC + nt * 8 + 2 * t4 + c;
+            if (col < a.kv_rank) out[static_cast<int64_t>(h) * a.kv_rank + col] = __float2bfloat16_rn(acc[q][nt][2 * half + c] * inv);
+          }
+      }
+    }
   }
 }
 
+template <int NT2, int TQ>
+int launch_attn_mma_tq(const AttnArgs& a, cudaStream_t st) {
+  const int DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 128;
+  const int DPS = (DP16 > RP ? DP16 : RP) + 8;
+  const size_t smem = static_cast<size_t>(TQ * 16 + 2 * kMmaKeys) * DPS * 2 + TQ * 16 * kPsStride * 2 +
+                      (TQ * 2 * 16 * kSsStride + TQ * 48) * 4;
+  NVLLM_SMEM_ATTR_ONCE((latent_attn_mma_kernel<NT2, TQ>), 225 * 1024);
+  dim3 grid((a.n + TQ - 1) / TQ, (a.heads + 15) / 16);
+  latent_attn_mma_kernel<NT2, TQ><<<grid, kMmaThreads, smem, st>>>(a, DPS, DP16);
+  NVLLM_LAUNCH_CHECK("latent_attn_mma_kernel");
+  return 0;
+}
+
+// Two tokens per CTA for batches that are mostly prompt portions (more than 256 tokens: a decode batch holds one token per
+// sequence, so its neighbours never share keys), when the second token's buffers still fit in shared memory.
 template <int NT2>
 int launch_attn_mma(const AttnArgs& a, cudaStream_t st) {
   const int DP16 = (static_cast<int>(a.cache_row) + 15) / 16 * 16, RP = NT2 * 128;
   const int DPS = (DP16 > RP ? DP16 : RP) + 8;
-  const size_t smem = static_cast<size_t>(16 + 2 * kMmaKeys) * DPS * 2 + 16 * kPsStride * 2 + (2 * 16 * kSsStride + 48) * 4;
-  NVLLM_SMEM_ATTR_ONCE((latent_attn_mma_kernel<NT2>), 220 * 1024);
-  dim3 grid(a.n, (a.heads + 15) / 16);
-  latent_attn_mma_kernel<NT2><<<grid, kMmaThreads, smem, st>>>(a, DPS, DP16);
-  NVLLM_LAUNCH_CHECK("latent_attn_mma_kernel");
-  return 0;
+  const size_t smem2 = static_cast<size_t>(32 + 2 * kMmaKeys) * DPS * 2 + 32 * kPsStride * 2 + (4 * 16 * kSsStride + 96) * 4;
+  if (a.n > 256 && knobs().latent_mma != 2 && smem2 <= 225 * 1024) return launch_attn_mma_tq<NT2, 2>(a, st);
+  return launch_attn_mma_tq<NT2, 1>(a, st);
 }
 
 template <typename T>

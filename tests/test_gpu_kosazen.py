@@ -490,8 +490,9 @@ def test_grouped_tensor_core_gemm(cuda):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_latent_attention_whole_prompts_in_one_launch(cuda, dtype):
-    """Every position of several sequences as a query in ONE launch (whole prompts side by side): odd and even lengths,
-    a one-token sequence, sequences that end inside and exactly on a page."""
+    """Every position of several sequences as a query in ONE launch of more than 256 tokens (the bf16 kernel then takes two
+    neighbouring tokens per CTA): odd and even lengths and a one-token sequence, so that pairs fall inside a sequence, on a
+    sequence's last token and across two sequences."""
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(16)
     H, dim, rd, r, bs, scale = 3, 8, 6, 40, 16, 0.3
@@ -502,6 +503,7 @@ def test_latent_attention_whole_prompts_in_one_launch(cuda, dtype):
     tok_seq = np.concatenate([np.full(c, b) for b, c in enumerate(ctx)]).astype(np.int32)
     pos = np.concatenate([np.arange(c) for c in ctx]).astype(np.int64)
     n = len(pos)
+    assert n > 256
     q_abs = rng.standard_normal((n, H, r)).astype(np.float32)
     q = K.bf16_round(rng.standard_normal((n, H, dim + rd)))
     out = ops.latent_attention(dev_t(q_abs.reshape(n, -1), cuda, torch.float32), dev_t(q.reshape(n, -1), cuda, dtype),
