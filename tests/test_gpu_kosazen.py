@@ -138,13 +138,14 @@ def _paged_case(rng, ctx, bs, row, extra=3):
     return cache, tables, seqs
 
 
+@pytest.mark.parametrize("H", [5, 19])   # 19 heads: more than one head group per token in both kernels
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_latent_attention_paged_positions(cuda, dtype):
+def test_latent_attention_paged_positions(cuda, dtype, H):
     """Queries at the first positions, just before / at / after page borders and deep into long sequences; several query
     tokens of one sequence in one launch (a prompt portion) beside single tokens of others."""
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(5)
-    H, dim, rd, r, bs, scale = 5, 9, 6, 40, 16, 0.21
+    dim, rd, r, bs, scale = 9, 6, 40, 16, 0.21
     ctx = [1, 15, 16, 17, 33, 150, 331]
     cache, tables, seqs = _paged_case(rng, ctx, bs, r + rd)
     if dtype == torch.bfloat16:
@@ -275,6 +276,9 @@ VARIANTS = {
     # sizes the tensor-core GEMM takes (k % 64, n % 8); a layer without feed-forward; no identity experts, no shared expert, top 1
     "aligned_plain": dict(vocab=128, width=64, n_layers=3, mlp_mask=[1, 0, 1], heads=2, dim=32, rot_dim=8, vdim=32, kv_rank=24,
                           ff=64, experts=4, identity=0, top=1, shared=False, router_scale=1.0),
+    # nothing divisible by 8, 4 or 2 except the rotated pairs; odd vocabulary
+    "primes": dict(vocab=101, width=37, n_layers=2, heads=3, dim=7, rot_dim=4, vdim=5, kv_rank=11, ff=13, shared_ff=9, experts=3,
+                   identity=1, top=2),
     # one head, one real expert, every router output chosen, loop that covers everything once
     "ones": dict(n_layers=2, loop=(0, 2, 1), heads=1, dim=8, rot_dim=8, vdim=8, kv_rank=8, experts=1, identity=1, top=2, ff=8, shared_ff=8, width=8),
 }
@@ -351,7 +355,7 @@ def test_engine_schedules_match_the_oracle(cuda, tmp_path, variant, dtype):
     def check(got, what):
         for i, r in enumerate(ref):
             e = rel_err(got[i], r)
-            assert np.isfinite(e).all() and e[sure[i]].max() < tol, \
+            assert np.isfinite(e).all() and (e[sure[i]].max() if sure[i].any() else 0.0) < tol, \
                 f"{variant} {dtype} {what}: request {i} position {int(e.argmax())} error {e.max():.3g}"
 
     whole = replay(eng, reqs, [[(i, len(r))] for i, r in enumerate(reqs)])
@@ -362,7 +366,7 @@ def test_engine_schedules_match_the_oracle(cuda, tmp_path, variant, dtype):
     # everything token by token
     one = replay(eng, reqs[:3], [[(i, 1)] for i, r in enumerate(reqs[:3]) for _ in r])
     for i in range(3):
-        assert rel_err(one[i], ref[i])[sure[i]].max() < tol
+        assert not sure[i].any() or rel_err(one[i], ref[i])[sure[i]].max() < tol
     # portions of changing size down to two tokens
     por = replay(eng, reqs, [[(i, c)] for i, r in enumerate(reqs) for c in cut(len(r), [2, 5, 16, 3, 17, 2, 31])])
     check(por, "portions")
@@ -401,7 +405,7 @@ def test_engine_mixed_batches_and_reused_pages(cuda, tmp_path, dtype):
     assert st["free_blocks"] == st["total_blocks"] == 11
     alone = replay(eng, reqs, [[(i, len(r))] for i, r in enumerate(reqs)])
     for i, r in enumerate(ref):
-        assert rel_err(mixed[i], r)[sure[i]].max() < TOL[dtype], (i, rel_err(mixed[i], r).max())
+        assert not sure[i].any() or rel_err(mixed[i], r)[sure[i]].max() < TOL[dtype], (i, rel_err(mixed[i], r).max())
         assert rel_err(mixed[i], alone[i].astype(np.float64)).max() < (1e-4 if dtype == "float32" else TOL[dtype])
 
 
