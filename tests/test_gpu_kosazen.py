@@ -526,3 +526,16 @@ def test_latent_attention_whole_prompts_in_one_launch(cuda, dtype):
             np.testing.assert_allclose(got[t0:t0 + c, h], ref, rtol=2e-2 if dtype == torch.bfloat16 else 1e-4,
                                        atol=2e-2 if dtype == torch.bfloat16 else 1e-5)
         t0 += c
+
+
+def test_long_prompt_takes_the_per_head_gemm_path(cuda, tmp_path):
+    """A bf16 prompt of more than 512 tokens with tensor-core sizes: the per-head projections run as one GEMM per head on
+    views of the packed activations, attention takes two tokens per CTA; then single tokens continue from that cache."""
+    rng = np.random.default_rng(17)
+    cfg = K.random_config(rng, vocab=64, width=64, n_layers=1, mlp_mask=[0], heads=2, dim=64, rot_dim=8, vdim=16, kv_rank=64, scale=0.12)
+    w = K.random_weights(cfg, rng)
+    toks = rng.integers(0, cfg["vocab"], 536).tolist()
+    ref = K.logits_of(cfg, w, toks)
+    eng, _ = make_engine(tmp_path, cfg, w, "bfloat16", bs=16, blocks=36, max_seqs=2)
+    got = replay(eng, [toks], [[(0, 530)]] + [[(0, 1)]] * 6)
+    assert rel_err(got[0], ref).max() < TOL["bfloat16"]
