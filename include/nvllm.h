@@ -351,8 +351,9 @@ int nvllm_linear(void* y, const void* x, const void* w, int32_t m, int32_t n, in
                  void* stream);
 /* Grouped variant for expert layers.  Rows are cut into 32-row tiles; tile i uses the weights of group tile_group[i]
  * (w + group * group_stride_w; < 0: tile unused).  row_src (nullable): row r reads x[row_src[r]] (< 0: padding row, not
- * written).  glu != 0: every group's weights are [gate rows (n) | up rows (n)] x k and the output is
- * min(g, limit) * sigmoid(1.702 * min(g, limit)) * (clamp(u, -limit, limit) + 1), g and u rounded to the operand type first. */
+ * written).  glu == 1: every group's weights are [gate rows (n) | up rows (n)] x k and the output is
+ * min(g, limit) * sigmoid(1.702 * min(g, limit)) * (clamp(u, -limit, limit) + 1), g and u rounded to the operand type first;
+ * glu == 2: the output is relu(v)^2 of the plain product v (rounded to the operand type first). */
 int nvllm_linear_grouped(void* y, const void* x, const void* w, int32_t max_rows, int32_t n, int32_t k, int64_t ldx,
                          int64_t ldw, int64_t ldy, int64_t group_stride_w, const int32_t* row_src,
                          const int32_t* tile_group, int32_t glu, float limit, int32_t dtype, int32_t out_dtype,
@@ -414,6 +415,76 @@ int nvllm_gemm_bf16_grouped(void* y, const void* x, const void* w, int32_t max_r
 int nvllm_moe_combine(void* out, const void* expert_out, const void* x, const void* shared_out, const int32_t* topk_idx,
                       const float* topk_w, const int32_t* slot_row, int32_t n, int32_t hidden, int32_t top, int32_t experts,
                       int32_t dtype, void* stream);
+
+/* ---- Parallel blocks on an f32 residual stream; attention with a score cap; mixers with a recurrent state ---------- */
+
+/* h += s0 a0 + s1 a1 + s2 a2 + bias_scale * bias (each addend [n, hidden], f32 or bf16 per its dt, nullable; bias f32
+ * [hidden], nullable), then out = (h - mean) / sqrt(var + eps) * w in out_dtype (out nullable: only the sum).  var is the
+ * mean of the squared deviations; all statistics f32. */
+int nvllm_residual_layernorm(void* out, float* h, const void* a0, float s0, int32_t dt0, const void* a1, float s1,
+                             int32_t dt1, const void* a2, float s2, int32_t dt2, const float* bias, float bias_scale,
+                             const float* w, int32_t n, int32_t hidden, float eps, int32_t out_dtype, void* stream);
+/* out[i, :] = [a[i, :] | b[i, :]] (f32 inputs) in out_dtype. */
+int nvllm_concat_cast(void* out, const float* a, const float* b, int32_t n, int32_t width_a, int32_t width_b,
+                      int32_t out_dtype, void* stream);
+/* h[i, :] = h_copy[i, :] (nullable) = table[ids[i], :] * scale as f32 (ids clamped to the table). */
+int nvllm_embedding_gather_scaled(float* h, float* h_copy, const void* table, const int64_t* ids, int32_t n,
+                                  int32_t hidden, int32_t vocab, float scale, int32_t table_dtype, void* stream);
+/* out[i, c] = silu(in[i, c]) * in[i, ff + c] (kind 0, in: [n, 2 ff]) or relu(in[i, c])^2 (kind 1, in: [n, ff]). */
+int nvllm_ff_activation(void* out, const void* in, int32_t n, int32_t ff, int32_t kind, int32_t dtype, void* stream);
+/* Expert choice by table: topk_idx[t, :] = table[ids[t], :] ([table_rows, top] int32), topk_w = 1 / top. */
+int nvllm_moe_table_route(int32_t* topk_idx, float* topk_w, const int32_t* table, const int64_t* ids, int32_t n,
+                          int32_t top, int32_t table_rows, void* stream);
+
+/* Attention preparation.  proj: f32 [n, >= q_cols + k_cols + v_cols] rows [q | k | v | ...]; adds the biases (nullable),
+ * writes q in `dtype` and k / v into cache rows slots[i] (k_row / v_row elements apart; slot < 0: nothing stored). */
+int nvllm_attn_bias_store(void* q, int64_t ldq, void* k_cache, void* v_cache, int64_t k_row, int64_t v_row,
+                          const float* proj, int64_t ldp, const float* q_bias, const float* k_bias, const float* v_bias,
+                          const int32_t* slots, int32_t n, int32_t q_cols, int32_t k_cols, int32_t v_cols, int32_t dtype,
+                          void* stream);
+/* Grouped-query softmax attention over the paged cache, without rotary:
+ *   s[t, h, j] = cap(scale * temp(p_t) * q[t, h] . k[j, h / (heads / kv_heads)]),  j <= p_t = positions[t] in sequence tok_seq[t]
+ *   temp(p) = 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1),  cap(s) = softcap * tanh(s / softcap) (softcap <= 0: s)
+ *   out[t, h, :] = sum_j softmax_j(s) v[j, ...] * sigmoid(gate[t, h, :])   (gate: f32, nullable)
+ * Key size dim, value size vdim (<= 256).  block_tables: [sequences, table_cap]. */
+int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
+                           const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
+                           const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
+                           int32_t table_cap, int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
+                           int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every, int32_t dtype,
+                           void* stream);
+
+/* Recurrent mixers.  A step lists its sequences: seq_slot[s] = the state slot of sequence s (< 0: padding, output zero),
+ * cu_tokens[s] .. cu_tokens[s + 1] = its tokens in the batch (in order of position), positions[] per token.  A portion
+ * whose first position is 0 starts from a zero state, any other from the slot's content; the slot is updated.  All f32.
+ *
+ * S_t = a_t S_(t-1) + b_t k_t v_t^T,  y_t = S_t^T q_t + skip_h v_t;  S: [dk, dv] per head; state: [slots, heads, dk, dv].
+ * q, k: [n, groups * dk] (head h reads group h / (heads / groups)); v, y: [n, heads * dv]; decay / step: [n, heads] when
+ * *_per_token, else [heads]; step nullable (1), skip nullable (0).  dk <= 256. */
+int nvllm_linear_recurrence(float* y, int64_t ldy, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v,
+                            int64_t ldv, const float* decay, int32_t decay_per_token, const float* step,
+                            int32_t step_per_token, const float* skip, float* state, const int32_t* seq_slot,
+                            const int32_t* cu_tokens, const int64_t* positions, int32_t n_seqs, int32_t heads,
+                            int32_t groups, int32_t dk, int32_t dv, void* stream);
+/* out[t, c] = act(bias[c] + sum_j w[c, j] * in[token at position(t) - (taps - 1 - j), c]) (zero before the sequence; act =
+ * SiLU when silu != 0); state: [slots, taps - 1, channels] = the raw inputs of the last taps - 1 tokens, read for inputs
+ * before the portion and rewritten afterwards.  taps <= 16; out != in. */
+int nvllm_causal_conv(float* out, int64_t ldo, const float* in, int64_t ldi, const float* w, const float* bias, float* state,
+                      const int32_t* tok_seq, const int32_t* seq_slot, const int32_t* cu_tokens, const int64_t* positions,
+                      int32_t n, int32_t n_seqs, int32_t channels, int32_t taps, int32_t silu, void* stream);
+/* step[t, h] = softplus(dt_raw[t, h] + dt_bias[h]);  decay[t, h] = exp(-exp(a_log[h]) * step[t, h]). */
+int nvllm_ssd_prepare(float* step, float* decay, const float* dt_raw, int64_t ld_raw, const float* dt_bias, const float* a_log,
+                      int32_t n, int32_t heads, void* stream);
+/* Rotary positions with the half-split pairing, in place on f32 rows [n, heads * dim]: within a head, value i < dims / 2 is
+ * paired with i + dims / 2, (u, v) -> (u cos - v sin, v cos + u sin), angle = position * base^(-2i/dims) from `table`
+ * ([max_pos, dims/2, 2], as nvllm_rope_table_interleaved builds); values beyond dims pass; the whole head is multiplied by scale. */
+int nvllm_rotate_half(float* x, int64_t ldx, const int64_t* positions, const float* table, int32_t max_pos, int32_t n,
+                      int32_t heads, int32_t dim, int32_t dims, float scale, void* stream);
+/* RMS norm over `parts` equal parts of every row (each by its own root mean square, eps inside the root) with a SiLU gate:
+ * gate_first != 0: t = y * silu(gate), out = t / rms(t) * w;   else: out = y / rms(y) * silu(gate) * w.   w nullable (1). */
+int nvllm_gated_group_norm(void* out, int64_t ldo, const float* y, int64_t ldy, const float* gate, int64_t ldg, const float* w,
+                           int32_t n, int32_t cols, int32_t parts, float eps, int32_t gate_first, int32_t out_dtype,
+                           void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Engine-level C ABI: the C++ host runtime that mirrors the reference's Rust types one-to-one

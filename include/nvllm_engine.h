@@ -38,7 +38,9 @@ typedef struct nvllm_config {
   int32_t kv_layout;              /* 0 = head-major [blk,Hkv,bs,D] (engine default), 1 = reference [blk,bs,Hkv,D] */
   int32_t sampling_seed;          /* engine seed of the sampler's counter-based uniforms (nvllm.h, nvllm_sample) */
   float rms_norm_eps;
-  float reserved_f;
+  int32_t recurrent_state;        /* 1: the model keeps a fixed-size state per sequence besides the paged cache.  Every sequence
+                                   * that holds cache blocks then also holds one of max_num_seqs state slots (admission waits
+                                   * for a free one) and prompts never share cached blocks: a state cannot be rebuilt from them */
   double rope_theta;
 } nvllm_config;
 
@@ -87,6 +89,8 @@ typedef struct nvllm_batch {
    * NULL = the last token of every sequence.  With explicit rows, the step's next tokens are chosen from the first
    * min(num_logit_rows, num_seqs) rows, so a caller that samples lists every sequence's last token first. */
   const int32_t* logit_rows;
+  /* [num_seqs] state slot of every sequence (models with recurrent_state; NULL otherwise). */
+  const int32_t* state_slots;
 } nvllm_batch;
 
 /* Scheduler (scheduler.rs:14-334) owning a BlockManager (block_manager.rs:69-331) and the Sequences
@@ -163,7 +167,8 @@ int nvllm_runner_layer_tap(nvllm_runner* r, float* h_buf);
 /* Seeded synthetic weights (nvllm_init_weight semantics per logical tensor, sliced per rank; norm weights = 1). */
 int nvllm_runner_init_weights(nvllm_runner* r, uint64_t seed, float std);
 /* Loads one full (unsharded) HF-named tensor from host bf16 memory; the runner keeps its TP slice and packs
- * q/k/v -> qkv_proj, gate/up -> gate_up_proj (utils/loader.rs:175-198; linear.rs:154-172,249-267). */
+ * q/k/v -> qkv_proj, gate/up -> gate_up_proj (utils/loader.rs:175-198; linear.rs:154-172,249-267).  Integer tables of
+ * registered architectures (tensors named `...table`) are passed as int32 instead. */
 int nvllm_runner_load_weight(nvllm_runner* r, const char* name, const void* h_bf16, int64_t rows, int64_t cols);
 /* ModelRunner::execute_model + sample_tokens (model_runner.rs:105-156): runs the forward for `batch`, writes the
  * sampled token of every sequence (greedy argmax, or nvllm_sample when any temperature != 0; the row seed of

@@ -77,6 +77,20 @@ PROTOTYPES = {
     "nvllm_gemm_bf16_push": (i32, [vp, vp, vp, vp, i32, i32, i32, i64, i64, i64, vp]),
     "nvllm_allreduce_add_rmsnorm_pushed": (i32, [vp, vp, vp, vp, vp, i32, i32, f32, i32, vp]),
     "nvllm_init_weight": (i32, [vp, i64, u64, u64, f32, i32, vp]),
+    "nvllm_residual_layernorm": (i32, [vp, vp, vp, f32, i32, vp, f32, i32, vp, f32, i32, vp, f32, vp, i32, i32, f32, i32, vp]),
+    "nvllm_concat_cast": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "nvllm_embedding_gather_scaled": (i32, [vp, vp, vp, vp, i32, i32, i32, f32, i32, vp]),
+    "nvllm_ff_activation": (i32, [vp, vp, i32, i32, i32, i32, vp]),
+    "nvllm_moe_table_route": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
+    "nvllm_attn_bias_store": (i32, [vp, i64, vp, vp, i64, i64, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "nvllm_capped_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                     f32, f32, f32, i32, i32, vp]),
+    "nvllm_linear_recurrence": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                      i32, vp]),
+    "nvllm_causal_conv": (i32, [vp, i64, vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "nvllm_ssd_prepare": (i32, [vp, vp, vp, i64, vp, vp, i32, i32, vp]),
+    "nvllm_rotate_half": (i32, [vp, i64, vp, vp, i32, i32, i32, i32, i32, f32, vp]),
+    "nvllm_gated_group_norm": (i32, [vp, i64, vp, i64, vp, i64, vp, i32, i32, i32, f32, i32, i32, vp]),
     "nvllm_linear": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i32, i64, i64, i64, i32, i32, vp]),
     "nvllm_linear_grouped": (i32, [vp, vp, vp, i32, i32, i32, i64, i64, i64, i64, vp, vp, i32, f32, i32, i32, vp]),
     "nvllm_glu_clamped": (i32, [vp, vp, i32, i32, f32, i32, vp]),

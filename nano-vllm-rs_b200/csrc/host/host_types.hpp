@@ -71,6 +71,7 @@ struct Sequence {
   int32_t num_cached_tokens = 0;
   int32_t num_computed_tokens = 0;  // tokens whose cache rows are written (sequences stepped in portions, Scheduler::schedule_chunks)
   std::vector<int32_t> block_table;
+  int32_t state_slot = -1;          // slot of the sequence's recurrent state while it holds cache blocks (StateSlots), else -1
   nvllm_sampling_params sp{};
   int32_t block_size = 256;  // follows Config (the reference hard-codes 256, sequence.rs:99)
 
@@ -100,7 +101,8 @@ class BlockManager {
     bool is_free_listed = false;
   };
 
-  BlockManager(int32_t num_blocks, int32_t block_size) : block_size_(block_size), blocks_(num_blocks) {
+  BlockManager(int32_t num_blocks, int32_t block_size, bool sharing = true)
+      : block_size_(block_size), blocks_(num_blocks), sharing_(sharing) {
     if (num_blocks <= 0 || block_size <= 0) throw std::invalid_argument("BlockManager: sizes must be positive");
     for (int32_t i = 0; i < num_blocks; ++i) push_back_free(i);  // free list = 0..n-1 (:96)
   }
@@ -120,9 +122,13 @@ class BlockManager {
   void allocate(Sequence& s) {
     if (!s.block_table.empty()) throw std::runtime_error("Sequence already has allocated blocks");
     if (!can_allocate(s)) throw std::runtime_error("Not enough free blocks to allocate sequence");
+    const int32_t nb = s.num_blocks();
+    if (!sharing_) {  // no prefix reuse: fresh, unhashed blocks
+      for (int32_t bi = 0; bi < nb; ++bi) s.block_table.push_back(take_front());
+      return;
+    }
     bool has_prefix = false, cache_miss = false;
     uint64_t prefix = 0;
-    const int32_t nb = s.num_blocks();
     for (int32_t bi = 0; bi < nb; ++bi) {
       const int32_t start = bi * block_size_;
       const int32_t n = std::min(block_size_, s.len() - start);
@@ -182,6 +188,10 @@ class BlockManager {
 
   void may_append(Sequence& s) {                                                           // :265-304
     if (s.block_table.empty()) throw std::runtime_error("Sequence has no allocated blocks");
+    if (!sharing_) {  // nothing is hashed: just cover the new token
+      while (static_cast<int32_t>(s.block_table.size()) < s.num_blocks()) s.block_table.push_back(take_front());
+      return;
+    }
     const int32_t last_id = s.block_table.back();
     Block& last = blocks_[last_id];
     const int32_t r = s.len() % block_size_;
@@ -244,8 +254,38 @@ class BlockManager {
 
   int32_t block_size_;
   std::vector<Block> blocks_;
+  bool sharing_ = true;
   std::unordered_map<uint64_t, int32_t> hash_to_block_;
   int32_t free_head_ = -1, free_tail_ = -1, free_count_ = 0;
+};
+
+// ---- StateSlots: the pool of per-sequence recurrent-state slots -------------------------------------------
+// Models whose mixers carry a fixed-size state (state-space, retention) keep it in one of `count` slots on the device; a
+// sequence takes a slot when it first gets cache blocks and returns it with them (finish, preemption).  Lowest free slot
+// first, so the assignment is reproducible.  A slot's content is never cleared on the host: the kernels start from zero
+// when a portion begins at position 0.
+class StateSlots {
+ public:
+  explicit StateSlots(int32_t count = 0) : used_(count > 0 ? count : 0, false) {}
+  bool enabled() const { return !used_.empty(); }
+  int32_t num_free() const {
+    int32_t n = 0;
+    for (bool u : used_) n += u ? 0 : 1;
+    return n;
+  }
+  int32_t take() {
+    for (size_t i = 0; i < used_.size(); ++i)
+      if (!used_[i]) { used_[i] = true; return static_cast<int32_t>(i); }
+    throw std::runtime_error("No free state slot");
+  }
+  void give(int32_t slot) {
+    if (slot < 0) return;
+    if (slot >= static_cast<int32_t>(used_.size()) || !used_[slot]) throw std::runtime_error("State slot is not in use");
+    used_[slot] = false;
+  }
+
+ private:
+  std::vector<bool> used_;
 };
 
 }  // namespace host

@@ -33,6 +33,8 @@ struct StepView {
   const int32_t* tok_seq = nullptr;   // row of `tables` of every token
   const int32_t* tables = nullptr;    // [n_seqs, table_cap]
   int table_cap = 0;
+  const int32_t* cu_tokens = nullptr;   // [n_seqs + 1] token range of every sequence in the step (tokens in order of position)
+  const int32_t* seq_slots = nullptr;   // [n_seqs] recurrent-state slot of every sequence (< 0: padding sequence), or null
   const int32_t* logit_rows = nullptr;  // tokens whose logits are wanted
   int n_logit_rows = 0;
   float* logits = nullptr;            // [n_logit_rows, vocab]
@@ -49,6 +51,8 @@ class ModelImpl {
   virtual int vocab() const = 0;
   virtual int hidden() const = 0;
   virtual int layer_runs() const = 0;
+  // true: the model keeps a fixed-size state per sequence in one of ModelLimits::max_seqs slots (StepView::seq_slots)
+  virtual bool recurrent_state() const { return false; }
   virtual int create(const ModelLimits& lim, cudaStream_t stream) = 0;
   virtual int init_weights(uint64_t seed, float std, cudaStream_t stream) = 0;
   virtual int load_weight(const char* name, const void* h_bf16, int64_t rows, int64_t cols, cudaStream_t stream) = 0;
@@ -64,5 +68,6 @@ ModelImpl* make_model(const json::Value& cfg);
 const char* registered_architectures();
 
 ModelImpl* make_kosazen(const json::Value& cfg);  // kosazen_model.cu
+ModelImpl* make_talapel(const json::Value& cfg);  // talapel_model.cu
 
 }  // namespace nvllm

@@ -129,6 +129,7 @@ struct nvllm_runner {
   std::unique_ptr<ModelImpl> model;
   int model_dtype = NVLLM_BF16;
   int32_t *d_tok_seq = nullptr, *d_logit_rows = nullptr;  // into d_meta: sequence of every token, tokens that feed the head
+  int32_t *d_cu_tokens = nullptr, *d_seq_slots = nullptr;  // into d_meta: token range and recurrent-state slot of every sequence
   int n_logit_rows = 0, logit_cap = 0;
   bool explicit_rows = false;
   float* layer_tap = nullptr;  // host memory (nullable): f32 residual stream after every layer run of eager steps
@@ -226,8 +227,8 @@ int nvllm_runner::create_for_model(const nvllm_config& c) {
   RUN(ensure_logit_rows(max_seqs));
   RUN(dalloc(&tokens, max_seqs));
   const size_t T = max_tokens, S = max_seqs;
-  const size_t prefill_meta = 28 * T + 8 * (S + 1) + 4 * S * table_cap;
-  const size_t decode_meta = S * (32 + 4 * static_cast<size_t>(table_cap));
+  const size_t prefill_meta = 28 * T + 8 * (S + 1) + 4 * S * table_cap + 4 * S;
+  const size_t decode_meta = S * (40 + 4 * static_cast<size_t>(table_cap)) + 8;
   meta_bytes = (prefill_meta > decode_meta ? prefill_meta : decode_meta) + 64;
   RUN(dalloc(&d_meta, meta_bytes));
   NVLLM_CUDA(cudaMallocHost(reinterpret_cast<void**>(&h_meta), meta_bytes));
@@ -253,6 +254,7 @@ int nvllm_runner::forward_model(int N, int S) {
   v.stream = stream; v.n_tokens = N; v.n_seqs = S;
   v.ids = d_ids; v.positions = d_pos; v.slots = d_slots; v.tok_seq = d_tok_seq; v.tables = d_tables; v.table_cap = table_cap;
   v.logit_rows = d_logit_rows; v.n_logit_rows = n_logit_rows; v.logits = logits;
+  v.cu_tokens = d_cu_tokens; v.seq_slots = d_seq_slots;
   cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
   v.capturing = cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone;
   v.layer_tap = layer_tap;
@@ -359,8 +361,8 @@ int nvllm_runner::create(const nvllm_config& c, nvllm_comm* cm) {
   if (decode_ws_bytes) { uint8_t* p = nullptr; RUN(dalloc(&p, decode_ws_bytes)); decode_ws = p; }
   // metadata
   const size_t S = max_seqs;
-  const size_t prefill_meta = 28 * T + 8 * (S + 1) + 4 * S * table_cap;
-  const size_t decode_meta = S * (32 + 4 * static_cast<size_t>(table_cap));
+  const size_t prefill_meta = 28 * T + 8 * (S + 1) + 4 * S * table_cap + 4 * S;
+  const size_t decode_meta = S * (40 + 4 * static_cast<size_t>(table_cap)) + 8;
   meta_bytes = (prefill_meta > decode_meta ? prefill_meta : decode_meta) + 64;
   RUN(dalloc(&d_meta, meta_bytes));
   NVLLM_CUDA(cudaMallocHost(reinterpret_cast<void**>(&h_meta), meta_bytes));
@@ -535,6 +537,14 @@ int nvllm_runner::upload(const nvllm_batch& b, int padded) {
       }
       o += 4 * static_cast<size_t>(n_logit_rows);
     }
+    d_cu_tokens = d_cu_q;
+    d_seq_slots = nullptr;
+    if (model && model->recurrent_state()) {
+      NVLLM_CHECK_ARG(b.state_slots != nullptr, NVLLM_ERR_ARG, "execute: this model needs a state slot per sequence (nvllm_batch.state_slots)");
+      for (size_t i = 0; i < S; ++i)
+        NVLLM_CHECK_ARG(b.state_slots[i] >= 0 && b.state_slots[i] < max_seqs, NVLLM_ERR_ARG, "execute: state slot %d out of range", b.state_slots[i]);
+      d_seq_slots = reinterpret_cast<int32_t*>(d_meta + put(b.state_slots, 4 * S));
+    }
     used = o;
   } else {
     const size_t B = b.num_seqs, P = padded;
@@ -569,6 +579,20 @@ int nvllm_runner::upload(const nvllm_batch& b, int padded) {
       used += 8 * P;
       n_logit_rows = static_cast<int>(P);
       explicit_rows = false;
+    }
+    d_cu_tokens = d_seq_slots = nullptr;
+    if (model) {  // token range of sequence i = [i, i + 1); padding sequences have no state slot
+      int32_t* cu = reinterpret_cast<int32_t*>(h_meta + used);
+      d_cu_tokens = reinterpret_cast<int32_t*>(d_meta + used);
+      for (size_t i = 0; i <= P; ++i) cu[i] = static_cast<int32_t>(i);
+      used += 4 * (P + 1);
+      if (model->recurrent_state()) {
+        NVLLM_CHECK_ARG(b.state_slots != nullptr, NVLLM_ERR_ARG, "execute: this model needs a state slot per sequence (nvllm_batch.state_slots)");
+        int32_t* ss = reinterpret_cast<int32_t*>(h_meta + used);
+        d_seq_slots = reinterpret_cast<int32_t*>(d_meta + used);
+        for (size_t i = 0; i < P; ++i) ss[i] = i < B ? b.state_slots[i] : -1;
+        used += 4 * P;
+      }
     }
     last_decode_b = static_cast<int>(P);
     last_ctx.assign(ctx, ctx + P);
@@ -863,6 +887,7 @@ int nvllm_config_init_for_model(nvllm_config* cfg, const char* model_config_json
   // the Qwen3-only fields carry no meaning for a registered architecture
   cfg->intermediate_size = 0; cfg->num_attention_heads = 0; cfg->num_key_value_heads = 0; cfg->head_dim = 0;
   cfg->qk_norm = 0; cfg->tie_word_embeddings = 0; cfg->max_position_embeddings = cfg->max_model_len;
+  cfg->recurrent_state = m->recurrent_state() ? 1 : 0;
   return 0;
 }
 int nvllm_runner_destroy(nvllm_runner* r) {

@@ -15,6 +15,7 @@ struct BatchArrays {
   std::vector<int32_t> slot_mapping, cu_q, cu_k, context_lens, block_tables;
   std::vector<float> temperatures, top_p;
   std::vector<int32_t> top_k;
+  std::vector<int32_t> state_slots;  // recurrent-state slot of every scheduled sequence (models with such a state)
   std::vector<int32_t> seq_index;  // slab indices of the scheduled sequences (postprocess order)
 };
 
@@ -23,7 +24,8 @@ class Scheduler {
   explicit Scheduler(const nvllm_config& c)
       : max_num_seqs_(c.max_num_seqs), max_num_batched_tokens_(c.max_num_batched_tokens),
         max_model_len_(c.max_model_len), eos_(c.eos_token_id), block_size_(c.kvcache_block_size),
-        bm_(c.num_kvcache_blocks > 0 ? c.num_kvcache_blocks : 1000, c.kvcache_block_size) {}  // :71-74
+        bm_(c.num_kvcache_blocks > 0 ? c.num_kvcache_blocks : 1000, c.kvcache_block_size, c.recurrent_state == 0),  // :71-74
+        states_(c.recurrent_state != 0 ? c.max_num_seqs : 0) {}
 
   BlockManager& block_manager() { return bm_; }
   const BlockManager& block_manager() const { return bm_; }
@@ -111,6 +113,11 @@ class Scheduler {
     }
     if (total > max_num_batched_tokens_) throw std::invalid_argument("schedule_chunks: step exceeds max_num_batched_tokens");
     if (need_blocks > bm_.num_free()) throw std::runtime_error("schedule_chunks: not enough free cache blocks");
+    if (states_.enabled()) {
+      int32_t need_states = 0;
+      for (int32_t i = 0; i < n; ++i) need_states += seqs_[slots[i]].state_slot < 0 ? 1 : 0;
+      if (need_states > states_.num_free()) throw std::runtime_error("schedule_chunks: not enough free state slots");
+    }
     arrays_.seq_index.assign(slots.begin(), slots.end());
     chunk_counts_.assign(counts, counts + n);
     for (int32_t i = 0; i < n; ++i) {
@@ -121,6 +128,10 @@ class Scheduler {
         running_.push_back(slots[i]);
       }
       bm_.grow(s, s.num_computed_tokens + counts[i]);
+      if (states_.enabled() && s.state_slot < 0) {
+        if (s.num_computed_tokens != 0) throw std::runtime_error("schedule_chunks: sequence lost its state slot mid-way");
+        s.state_slot = states_.take();
+      }
     }
     ++prefill_batches_;
     fill_common(out, true);
@@ -165,6 +176,7 @@ class Scheduler {
     Sequence& s = seqs_[si];
     s.status = Status::Finished;
     if (!s.block_table.empty()) bm_.deallocate(s);
+    drop_state(s);
     s.num_computed_tokens = 0;
     running_.erase(std::remove(running_.begin(), running_.end(), si), running_.end());
     waiting_.erase(std::remove(waiting_.begin(), waiting_.end(), si), waiting_.end());
@@ -195,6 +207,7 @@ class Scheduler {
       if (s.should_stop(eos_)) {
         s.status = Status::Finished;
         bm_.deallocate(s);
+        drop_state(s);
         running_.erase(std::remove(running_.begin(), running_.end(), si), running_.end());    // :260-262
         ++finished_;
       }
@@ -221,9 +234,11 @@ class Scheduler {
       const int32_t seq_tokens = s.len() - s.num_cached_tokens;                               // :135 (before allocate)
       if (num_batched + seq_tokens > max_num_batched_tokens_) break;                          // :136 strict >
       if (!bm_.can_allocate(s)) break;                                                        // :141
+      if (states_.enabled() && states_.num_free() == 0) break;   // every state slot is held by a running sequence
       sched.push_back(waiting_.front());
       waiting_.pop_front();
       bm_.allocate(s);                                                                        // :149
+      if (states_.enabled()) s.state_slot = states_.take();
       ++num_seqs;
       num_batched += seq_tokens;
       s.status = Status::Running;
@@ -263,18 +278,25 @@ class Scheduler {
     Sequence& s = seqs_[si];
     s.status = Status::Preempted;
     bm_.deallocate(s);
+    drop_state(s);   // recomputed from position 0 when it is admitted again
     waiting_.push_front(si);
     ++preemptions_;
+  }
+
+  void drop_state(Sequence& s) {
+    if (s.state_slot >= 0) { states_.give(s.state_slot); s.state_slot = -1; }
   }
 
   void fill_common(nvllm_batch* out, bool is_prefill) {
     BatchArrays& a = arrays_;
     const int32_t n = static_cast<int32_t>(a.seq_index.size());
     a.seq_ids.resize(n);
+    a.state_slots.resize(n);
     a.temperatures.resize(n); a.top_k.resize(n); a.top_p.resize(n);
     for (int32_t i = 0; i < n; ++i) {                                                         // model_runner.rs:137-146
       const Sequence& s = seqs_[a.seq_index[i]];
       a.seq_ids[i] = s.seq_id;
+      a.state_slots[i] = s.state_slot;
       a.temperatures[i] = s.sp.temperature;
       a.top_k[i] = s.sp.top_k;
       a.top_p[i] = s.sp.top_p;
@@ -286,6 +308,7 @@ class Scheduler {
     out->temperatures = a.temperatures.data();
     out->top_k = a.top_k.data();
     out->top_p = a.top_p.data();
+    out->state_slots = states_.enabled() ? a.state_slots.data() : nullptr;
   }
 
   void fill_tables(nvllm_batch* out) {                                                        // model_runner.rs:280-293
@@ -360,6 +383,7 @@ class Scheduler {
   int64_t eos_;
   int32_t block_size_;
   BlockManager bm_;
+  StateSlots states_;
   std::vector<Sequence> seqs_;           // slab; queues hold slab indices, id_to_slot_ maps seq_id -> index
   std::unordered_map<int64_t, int32_t> id_to_slot_;
   std::vector<int32_t> free_slots_;      // slab entries of released sequences, reused by add_sequence

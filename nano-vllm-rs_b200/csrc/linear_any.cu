@@ -18,6 +18,7 @@ struct LinArgs {
   const int32_t* tile_group;  // group (expert) of every 32-row tile; < 0 = tile unused.  w += group * bsw
   int64_t up_off;             // GLU: element offset of the `up` rows relative to the `gate` rows inside w
   float limit;                // GLU clamp
+  int act;                    // epilogue of the plain product: 0 none, 2 relu(v)^2
 };
 
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
@@ -109,6 +110,10 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
         float g = v, u = acu[i][j];
         if (sizeof(TI) == 2) { g = __bfloat162float(__float2bfloat16_rn(g)); u = __bfloat162float(__float2bfloat16_rn(u)); }
         v = glu_clamped(g, u, a.limit);
+      } else if (a.act == 2) {
+        if (sizeof(TI) == 2) v = __bfloat162float(__float2bfloat16_rn(v));
+        v = fmaxf(v, 0.f);
+        v *= v;
       }
       stf(y + static_cast<int64_t>(m) * a.ldy + n, v);
     }
@@ -149,6 +154,25 @@ __global__ void glu_clamped_vec8_kernel(bf16* __restrict__ out, const bf16* __re
   }
 }
 
+// kind 0: out[i, c] = silu(in[i, c]) * in[i, ff + c] (in: [n, 2 ff]);  kind 1: out[i, c] = relu(in[i, c])^2 (in: [n, ff])
+template <typename T>
+__global__ void ff_activation_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t n, int ff, int kind) {
+  const int64_t total = n * ff;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / ff, c = i - r * ff;
+    float v;
+    if (kind == 0) {
+      const float g = ldf(in + r * 2 * ff + c);
+      v = g / (1.0f + expf(-g)) * ldf(in + r * 2 * ff + ff + c);
+    } else {
+      v = fmaxf(ldf(in + i), 0.f);
+      v *= v;
+    }
+    stf(out + i, v);
+  }
+}
+
 template <bool GLU>
 int launch_tile(const LinArgs& a, int m_tiles, int batch, int dtype, int out_dtype, cudaStream_t st) {
   dim3 grid((a.N + BN - 1) / BN, m_tiles, batch);
@@ -178,7 +202,7 @@ extern "C" int nvllm_linear(void* y, const void* x, const void* w, int32_t m, in
   if (dtype == NVLLM_BF16 && batch == 1 && k % 64 == 0 && n % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldy % 8 == 0 &&
       aligned16(y) && aligned16(x) && aligned16(w))
     return nvllm_gemm_bf16(y, x, w, m, n, k, ldx, ldw, ldy, out_dtype, nullptr, 0, stream);
-  LinArgs a{y, x, w, m, n, k, ldx, ldw, ldy, bsx, bsw, bsy, nullptr, nullptr, 0, 0.f};
+  LinArgs a{y, x, w, m, n, k, ldx, ldw, ldy, bsx, bsw, bsy, nullptr, nullptr, 0, 0.f, 0};
   return launch_tile<false>(a, (m + BM - 1) / BM, batch, dtype, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
@@ -194,9 +218,9 @@ extern "C" int nvllm_linear_grouped(void* y, const void* x, const void* w, int32
   NVLLM_CHECK_ARG(y && x && w, NVLLM_ERR_ARG, "linear_grouped: NULL");
   // GLU: every group's weight block is [gate rows (n) | up rows (n)] x k
   LinArgs a{y, x, w, max_rows, n, k, ldx, ldw, ldy, 0, group_stride_w, 0, row_src, tile_group,
-            static_cast<int64_t>(n) * ldw, limit};
+            static_cast<int64_t>(n) * ldw, limit, glu == 2 ? 2 : 0};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return glu ? launch_tile<true>(a, max_rows / BM, 1, dtype, out_dtype, st)
+  return glu == 1 ? launch_tile<true>(a, max_rows / BM, 1, dtype, out_dtype, st)
              : launch_tile<false>(a, max_rows / BM, 1, dtype, out_dtype, st);
 }
 
@@ -219,5 +243,20 @@ extern "C" int nvllm_glu_clamped(void* out, const void* gate_up, int32_t n, int3
     glu_clamped_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), static_cast<const float*>(gate_up), n, ff, limit);
   else NVLLM_CHECK_ARG(false, NVLLM_ERR_DTYPE, "glu_clamped: dtype %d", dtype);
   NVLLM_LAUNCH_CHECK("glu_clamped_kernel");
+  return 0;
+}
+
+extern "C" int nvllm_ff_activation(void* out, const void* in, int32_t n, int32_t ff, int32_t kind, int32_t dtype, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && ff > 0 && (kind == 0 || kind == 1), NVLLM_ERR_ARG, "ff_activation: n=%d ff=%d kind=%d", n, ff, kind);
+  NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "ff_activation: dtype %d", dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(out && in, NVLLM_ERR_ARG, "ff_activation: NULL");
+  const int64_t total = static_cast<int64_t>(n) * ff;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == NVLLM_BF16) ff_activation_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<bf16*>(out), static_cast<const bf16*>(in), n, ff, kind);
+  else ff_activation_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), static_cast<const float*>(in), n, ff, kind);
+  NVLLM_LAUNCH_CHECK("ff_activation_kernel");
   return 0;
 }

@@ -165,10 +165,35 @@ __global__ void moe_combine_vec8_kernel(bf16* __restrict__ out, const bf16* __re
   }
 }
 
+// Routing without a router: row ids[t] of a table names the experts of token t, each with the same weight.
+__global__ void moe_table_route_kernel(int32_t* __restrict__ topk_idx, float* __restrict__ topk_w, const int32_t* __restrict__ table,
+                                       const int64_t* __restrict__ ids, int64_t n, int top, int rows, float weight) {
+  const int64_t total = n * top;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / top;
+    int64_t id = ids[t];
+    id = id < 0 ? 0 : (id >= rows ? rows - 1 : id);
+    topk_idx[i] = table[id * top + (i - t * top)];
+    topk_w[i] = weight;
+  }
+}
+
 }  // namespace
 }  // namespace nvllm
 
 using namespace nvllm;
+
+extern "C" int nvllm_moe_table_route(int32_t* topk_idx, float* topk_w, const int32_t* table, const int64_t* ids, int32_t n,
+                                     int32_t top, int32_t table_rows, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && top > 0 && table_rows > 0, NVLLM_ERR_ARG, "moe_table_route: n=%d top=%d rows=%d", n, top, table_rows);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(topk_idx && topk_w && table && ids, NVLLM_ERR_ARG, "moe_table_route: NULL");
+  const int64_t total = static_cast<int64_t>(n) * top;
+  moe_table_route_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(topk_idx, topk_w, table, ids, n,
+                                                                                                               top, table_rows, 1.0f / top);
+  NVLLM_LAUNCH_CHECK("moe_table_route_kernel");
+  return 0;
+}
 
 extern "C" int nvllm_moe_route(int32_t* topk_idx, float* topk_w, const float* logits, const float* bias, int32_t n,
                                int32_t e_total, int32_t top, float scale, void* stream) {

@@ -1,0 +1,348 @@
+// recurrence.cu — mixers that carry a fixed-size state from token to token instead of a growing cache.  The state of a
+// sequence lives in a SLOT of a state pool (f32) that the scheduler hands out when the sequence is admitted; a step names,
+// per sequence, its slot and the range of its tokens in the batch (cu_tokens), so one launch serves whole prompts, portions
+// and single decoded tokens.  A portion that begins at position 0 starts from a zero state (a reused slot needs no clearing);
+// any other portion continues from what the slot holds.
+//
+//   nvllm_linear_recurrence   S_t = a_t S_(t-1) + b_t k_t v_t^T,   y_t = S_t^T q_t + d v_t        (S: [dk, dv] per head)
+//       covers state-space duality (k = B, q = C, v = x, a = exp(-exp(A_log) dt), b = dt, d = D; B and C shared by the heads
+//       of a group) and retention (a = a constant per head, b = 1, d = 0)
+//   nvllm_causal_conv         per-channel convolution over the last `taps` tokens (+ bias, SiLU); the raw inputs of the last
+//       taps - 1 tokens are part of the state
+//   nvllm_ssd_prepare         dt = softplus(raw + bias), a = exp(-exp(A_log) dt)
+//   nvllm_rotate_half         rotary positions, dimension i paired with i + dims/2, on the first `dims` values of every head
+//   nvllm_gated_group_norm    RMS norm over equal parts of a row with a SiLU gate before or after it
+// Everything here is f32: inputs, state, arithmetic.  Only nvllm_gated_group_norm writes the operand type (its output
+// feeds a projection).
+#include "common.cuh"
+
+namespace nvllm {
+namespace {
+
+struct RecArgs {
+  float* y; int64_t ldy;
+  const float *q, *k, *v; int64_t ldq, ldk, ldv;
+  int group_div;                 // head h reads q / k of group h / group_div
+  const float* decay; int decay_ld;   // [n, heads] (decay_ld = heads) or [heads] (decay_ld = 0)
+  const float* step; int step_ld;     // same, or null (1)
+  const float* skip;                  // [heads] or null (0)
+  float* state;                       // [slots, heads, dk, dv]
+  const int32_t *seq_slot, *cu_tokens; const int64_t* positions;
+  int heads, dk, dv;
+};
+
+constexpr int kRecTile = 16;  // tokens staged per round
+
+// CTA = (head, sequence, slice of dv).  Thread (p, ns): column p of the state, rows [ns * NPT, (ns + 1) * NPT) in registers.
+// Per round, kRecTile tokens' k, q (rows of dk), v, a, b are staged in shared memory; the products need no further
+// synchronisation.  NSL row slices of one column sit in neighbouring lanes and are summed with shuffles.
+template <int NPT, int NSL>
+__global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a, int pb) {
+  extern __shared__ float sm[];
+  const int DKP = NPT * NSL;                       // padded dk
+  float* ks = sm;                                  // [tile][DKP]
+  float* qs = ks + kRecTile * DKP;                 // [tile][DKP]
+  float* vs = qs + kRecTile * DKP;                 // [tile][pb]
+  float* as = vs + kRecTile * pb;                  // [tile]
+  float* bs = as + kRecTile;                       // [tile]
+  const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * pb;
+  const int tid = threadIdx.x, ns = tid % NSL, pl = tid / NSL, p = p0 + pl;
+  const bool live = pl < pb && p < a.dv;
+  const int t0 = a.cu_tokens[s], t1 = a.cu_tokens[s + 1];
+  const int slot = a.seq_slot[s];
+  if (t1 <= t0) return;
+  if (slot < 0) {  // padding sequence of a captured batch: defined output, no state
+    for (int t = t0; t < t1; ++t)
+      if (live && ns == 0) a.y[t * a.ldy + static_cast<int64_t>(h) * a.dv + p] = 0.f;
+    return;
+  }
+  const int g = h / a.group_div;
+  float S[NPT];
+  float* sp = a.state + ((static_cast<int64_t>(slot) * a.heads + h) * a.dk) * a.dv;
+  const bool fresh = a.positions[t0] == 0;
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = ns * NPT + i;
+    S[i] = (!fresh && live && n < a.dk) ? sp[static_cast<int64_t>(n) * a.dv + p] : 0.f;
+  }
+  const float d = a.skip ? a.skip[h] : 0.f;
+  for (int tb = t0; tb < t1; tb += kRecTile) {
+    const int cnt = min(kRecTile, t1 - tb);
+    __syncthreads();
+    for (int e = tid; e < cnt * DKP; e += blockDim.x) {
+      const int tt = e / DKP, n = e % DKP;
+      const int64_t t = tb + tt;
+      ks[e] = n < a.dk ? a.k[t * a.ldk + static_cast<int64_t>(g) * a.dk + n] : 0.f;
+      qs[e] = n < a.dk ? a.q[t * a.ldq + static_cast<int64_t>(g) * a.dk + n] : 0.f;
+    }
+    for (int e = tid; e < cnt * pb; e += blockDim.x) {
+      const int tt = e / pb, c = e % pb;
+      vs[e] = p0 + c < a.dv ? a.v[(tb + tt) * a.ldv + static_cast<int64_t>(h) * a.dv + p0 + c] : 0.f;
+    }
+    if (tid < cnt) {
+      const int64_t t = tb + tid;
+      as[tid] = a.decay[a.decay_ld ? t * a.decay_ld + h : h];
+      bs[tid] = a.step ? a.step[a.step_ld ? t * a.step_ld + h : h] : 1.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float av = as[tt], xv = vs[tt * pb + (pl < pb ? pl : 0)], bv = bs[tt] * xv;
+      const float* kr = ks + tt * DKP + ns * NPT;
+      const float* qr = qs + tt * DKP + ns * NPT;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        S[i] = fmaf(av, S[i], bv * kr[i]);
+        acc = fmaf(S[i], qr[i], acc);
+      }
+#pragma unroll
+      for (int o = 1; o < NSL; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && ns == 0) a.y[(tb + tt) * a.ldy + static_cast<int64_t>(h) * a.dv + p] = fmaf(d, xv, acc);
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = ns * NPT + i;
+      if (n < a.dk) sp[static_cast<int64_t>(n) * a.dv + p] = S[i];
+    }
+  }
+}
+
+struct ConvArgs {
+  float* out; int64_t ldo;
+  const float* in; int64_t ldi;
+  const float *w, *b;        // [channels, taps], [channels]
+  float* state;              // [slots, taps - 1, channels]: raw inputs of the taps - 1 tokens before the next one, oldest first
+  const int32_t *tok_seq, *seq_slot, *cu_tokens; const int64_t* positions;
+  int n, channels, taps, silu;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+// out[t, c] = act(b[c] + sum_j w[c, j] * in(position(t) - (taps - 1 - j), c)); inputs before the portion come from the
+// state, inputs before the sequence are zero.
+__global__ void causal_conv_kernel(const ConvArgs a) {
+  const int64_t total = static_cast<int64_t>(a.n) * a.channels;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / a.channels), c = static_cast<int>(i % a.channels);
+    const int s = a.tok_seq[t], slot = a.seq_slot[s];
+    if (slot < 0) { a.out[t * a.ldo + c] = 0.f; continue; }
+    const int c0 = a.cu_tokens[s];
+    const int64_t p = a.positions[t], pf = a.positions[c0];
+    const float* st = a.state + static_cast<int64_t>(slot) * (a.taps - 1) * a.channels;
+    float acc = a.b ? a.b[c] : 0.f;
+    for (int j = 0; j < a.taps; ++j) {
+      const int back = a.taps - 1 - j;
+      const int64_t ps = p - back;
+      if (ps < 0) continue;
+      float x;
+      if (t - back >= c0) x = a.in[static_cast<int64_t>(t - back) * a.ldi + c];
+      else x = st[(ps - (pf - (a.taps - 1))) * a.channels + c];
+      acc = fmaf(a.w[static_cast<int64_t>(c) * a.taps + j], x, acc);
+    }
+    a.out[t * a.ldo + c] = a.silu ? silu_f(acc) : acc;
+  }
+}
+
+constexpr int kMaxTaps = 16;
+
+// After the convolution: the state becomes the raw inputs of the last taps - 1 positions (old state entries shift down when
+// the portion is shorter than that).  One thread per (sequence, channel).
+__global__ void conv_state_kernel(const ConvArgs a, int n_seqs) {
+  const int64_t total = static_cast<int64_t>(n_seqs) * a.channels;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int s = static_cast<int>(i / a.channels), c = static_cast<int>(i % a.channels);
+    const int slot = a.seq_slot[s], c0 = a.cu_tokens[s], len = a.cu_tokens[s + 1] - c0;
+    if (slot < 0 || len <= 0) continue;
+    const int64_t pf = a.positions[c0], pe = pf + len;
+    float* st = a.state + static_cast<int64_t>(slot) * (a.taps - 1) * a.channels;
+    float nv[kMaxTaps];
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) {
+      if (k >= a.taps - 1) break;
+      const int64_t ps = pe - (a.taps - 1) + k;
+      float x = 0.f;
+      if (ps >= pf) x = a.in[(c0 + (ps - pf)) * a.ldi + c];
+      else if (ps >= 0) x = st[(ps - (pf - (a.taps - 1))) * a.channels + c];
+      nv[k] = x;
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) {
+      if (k >= a.taps - 1) break;
+      st[static_cast<int64_t>(k) * a.channels + c] = nv[k];
+    }
+  }
+}
+
+__global__ void ssd_prepare_kernel(float* __restrict__ step, float* __restrict__ decay, const float* __restrict__ raw, int64_t ldr,
+                                   const float* __restrict__ dt_bias, const float* __restrict__ a_log, int64_t n, int heads) {
+  const int64_t total = n * heads;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t t = i / heads;
+    const int h = static_cast<int>(i - t * heads);
+    const float x = raw[t * ldr + h] + dt_bias[h];
+    const float dt = x > 20.f ? x : log1pf(expf(x));
+    step[i] = dt;
+    decay[i] = expf(-expf(a_log[h]) * dt);
+  }
+}
+
+// x[t, h * head_stride + i] for i < dims: (u, v) = (x[i], x[i + dims/2]) -> (u cos - v sin, v cos + u sin), then * scale (all
+// `dim` values of the head are scaled).  table: [max_pos, dims/2, 2] (cos, sin) from f64 angles.
+__global__ void rotate_half_kernel(float* __restrict__ x, int64_t ldx, const int64_t* __restrict__ positions, const float* __restrict__ table,
+                                   int max_pos, int64_t n, int heads, int dim, int dims, float scale) {
+  const int half = dims / 2, per = dim - half;  // work items per head: pairs + unrotated tail
+  const int64_t total = n * heads * per;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t th = i / per;
+    const int e = static_cast<int>(i - th * per);
+    const int64_t t = th / heads;
+    const int h = static_cast<int>(th - t * heads);
+    float* xh = x + t * ldx + static_cast<int64_t>(h) * dim;
+    if (e < half) {
+      int64_t p = positions[t];
+      p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+      const float2 cs = reinterpret_cast<const float2*>(table)[p * half + e];
+      const float u = xh[e], v = xh[e + half];
+      xh[e] = (u * cs.x - v * cs.y) * scale;
+      xh[e + half] = (v * cs.x + u * cs.y) * scale;
+    } else if (scale != 1.0f) {
+      xh[e + half] *= scale;
+    }
+  }
+}
+
+// One CTA per (token, part): parts of `gs` values.  gate_first: t = y * silu(z), out = rms(t) * w;  else out = rms(y) * silu(z) [* w].
+template <typename TO>
+__global__ void __launch_bounds__(128) gated_group_norm_kernel(TO* __restrict__ out, int64_t ldo, const float* __restrict__ y, int64_t ldy,
+                                                               const float* __restrict__ z, int64_t ldz, const float* __restrict__ w, int gs,
+                                                               int parts, float eps, int gate_first) {
+  __shared__ float red[4];
+  const int64_t t = blockIdx.x / parts;
+  const int g = blockIdx.x % parts;
+  const float* yr = y + t * ldy + static_cast<int64_t>(g) * gs;
+  const float* zr = z + t * ldz + static_cast<int64_t>(g) * gs;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    float v = yr[c];
+    if (gate_first) v *= silu_f(zr[c]);
+    sq = fmaf(v, v, sq);
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  const float r = rsqrtf((red[0] + red[1] + red[2] + red[3]) / gs + eps);
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    float v = yr[c];
+    const float sg = silu_f(zr[c]);
+    v = gate_first ? v * sg * r : v * r * sg;
+    if (w) v *= w[static_cast<int64_t>(g) * gs + c];
+    if (sizeof(TO) == 2) reinterpret_cast<bf16*>(out)[t * ldo + static_cast<int64_t>(g) * gs + c] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(out)[t * ldo + static_cast<int64_t>(g) * gs + c] = v;
+  }
+}
+
+inline unsigned grid_for(int64_t total) {
+  int64_t b = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  return static_cast<unsigned>(b > cap ? cap : (b < 1 ? 1 : b));
+}
+
+template <int NPT, int NSL>
+int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t st) {
+  int pb = a.dv;                                  // columns per CTA
+  const int max_pb = 512 / NSL;
+  if (pb > max_pb) pb = max_pb;
+  // more CTAs when few (sequence, head) pairs would leave SMs idle: split the columns (each column is independent)
+  while (pb > 32 && static_cast<int64_t>(a.heads) * n_seqs * ((a.dv + pb - 1) / pb) < sm_count() && pb % 2 == 0) pb /= 2;
+  const int threads = ((pb * NSL + 31) / 32) * 32;
+  const size_t smem = (static_cast<size_t>(kRecTile) * (2 * NPT * NSL + pb) + 2 * kRecTile) * sizeof(float);
+  dim3 grid(a.heads, n_seqs, (a.dv + pb - 1) / pb);
+  if (smem > 48 * 1024) NVLLM_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<NPT, NSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  linear_recurrence_kernel<NPT, NSL><<<grid, threads, smem, st>>>(a, pb);
+  NVLLM_LAUNCH_CHECK("linear_recurrence_kernel");
+  return 0;
+}
+
+}  // namespace
+}  // namespace nvllm
+
+using namespace nvllm;
+
+extern "C" int nvllm_linear_recurrence(float* y, int64_t ldy, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v,
+                                       int64_t ldv, const float* decay, int32_t decay_per_token, const float* step,
+                                       int32_t step_per_token, const float* skip, float* state, const int32_t* seq_slot,
+                                       const int32_t* cu_tokens, const int64_t* positions, int32_t n_seqs, int32_t heads,
+                                       int32_t groups, int32_t dk, int32_t dv, void* stream) {
+  NVLLM_CHECK_ARG(n_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dk <= 256 && dv > 0, NVLLM_ERR_ARG,
+                  "linear_recurrence: seqs=%d heads=%d groups=%d dk=%d (<= 256) dv=%d", n_seqs, heads, groups, dk, dv);
+  if (n_seqs == 0) return 0;
+  NVLLM_CHECK_ARG(y && q && k && v && decay && state && seq_slot && cu_tokens && positions, NVLLM_ERR_ARG, "linear_recurrence: NULL");
+  RecArgs a{y, ldy, q, k, v, ldq, ldk, ldv, heads / groups, decay, decay_per_token ? heads : 0, step, step_per_token ? heads : 0,
+            skip, state, seq_slot, cu_tokens, positions, heads, dk, dv};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dk <= 16) return launch_recurrence<16, 1>(a, n_seqs, st);
+  if (dk <= 32) return launch_recurrence<32, 1>(a, n_seqs, st);
+  if (dk <= 64) return launch_recurrence<64, 1>(a, n_seqs, st);
+  if (dk <= 128) return launch_recurrence<64, 2>(a, n_seqs, st);
+  return launch_recurrence<64, 4>(a, n_seqs, st);
+}
+
+extern "C" int nvllm_causal_conv(float* out, int64_t ldo, const float* in, int64_t ldi, const float* w, const float* bias, float* state,
+                                 const int32_t* tok_seq, const int32_t* seq_slot, const int32_t* cu_tokens, const int64_t* positions,
+                                 int32_t n, int32_t n_seqs, int32_t channels, int32_t taps, int32_t silu, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && n_seqs >= 0 && channels > 0 && taps >= 1 && taps <= kMaxTaps, NVLLM_ERR_ARG,
+                  "causal_conv: n=%d channels=%d taps=%d (1..16)", n, channels, taps);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(out && in && w && state && tok_seq && seq_slot && cu_tokens && positions && out != in, NVLLM_ERR_ARG, "causal_conv: NULL");
+  ConvArgs a{out, ldo, in, ldi, w, bias, state, tok_seq, seq_slot, cu_tokens, positions, n, channels, taps, silu};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  causal_conv_kernel<<<grid_for(static_cast<int64_t>(n) * channels), 256, 0, st>>>(a);
+  NVLLM_LAUNCH_CHECK("causal_conv_kernel");
+  if (taps > 1) {
+    conv_state_kernel<<<grid_for(static_cast<int64_t>(n_seqs) * channels), 256, 0, st>>>(a, n_seqs);
+    NVLLM_LAUNCH_CHECK("conv_state_kernel");
+  }
+  return 0;
+}
+
+extern "C" int nvllm_ssd_prepare(float* step, float* decay, const float* dt_raw, int64_t ld_raw, const float* dt_bias, const float* a_log,
+                                 int32_t n, int32_t heads, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && heads > 0 && ld_raw >= heads, NVLLM_ERR_ARG, "ssd_prepare: sizes");
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(step && decay && dt_raw && dt_bias && a_log, NVLLM_ERR_ARG, "ssd_prepare: NULL");
+  ssd_prepare_kernel<<<grid_for(static_cast<int64_t>(n) * heads), 256, 0, static_cast<cudaStream_t>(stream)>>>(step, decay, dt_raw, ld_raw, dt_bias,
+                                                                                                           a_log, n, heads);
+  NVLLM_LAUNCH_CHECK("ssd_prepare_kernel");
+  return 0;
+}
+
+extern "C" int nvllm_rotate_half(float* x, int64_t ldx, const int64_t* positions, const float* table, int32_t max_pos, int32_t n,
+                                 int32_t heads, int32_t dim, int32_t dims, float scale, void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && heads > 0 && dim > 0 && dims >= 0 && dims % 2 == 0 && dims <= dim && max_pos > 0, NVLLM_ERR_ARG,
+                  "rotate_half: heads=%d dim=%d dims=%d", heads, dim, dims);
+  if (n == 0 || (dims == 0 && scale == 1.0f)) return 0;
+  NVLLM_CHECK_ARG(x && positions && (table || dims == 0), NVLLM_ERR_ARG, "rotate_half: NULL");
+  const int64_t total = static_cast<int64_t>(n) * heads * (dim - dims / 2);
+  rotate_half_kernel<<<grid_for(total), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, ldx, positions, table, max_pos, n, heads, dim, dims, scale);
+  NVLLM_LAUNCH_CHECK("rotate_half_kernel");
+  return 0;
+}
+
+extern "C" int nvllm_gated_group_norm(void* out, int64_t ldo, const float* y, int64_t ldy, const float* gate, int64_t ldg, const float* w,
+                                      int32_t n, int32_t cols, int32_t parts, float eps, int32_t gate_first, int32_t out_dtype,
+                                      void* stream) {
+  NVLLM_CHECK_ARG(n >= 0 && cols > 0 && parts > 0 && cols % parts == 0, NVLLM_ERR_ARG, "gated_group_norm: cols=%d parts=%d", cols, parts);
+  NVLLM_CHECK_ARG(out_dtype == NVLLM_BF16 || out_dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "gated_group_norm: dtype %d", out_dtype);
+  if (n == 0) return 0;
+  NVLLM_CHECK_ARG(out && y && gate, NVLLM_ERR_ARG, "gated_group_norm: NULL");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(static_cast<int64_t>(n) * parts);
+  if (out_dtype == NVLLM_BF16)
+    gated_group_norm_kernel<bf16><<<grid, 128, 0, st>>>(static_cast<bf16*>(out), ldo, y, ldy, gate, ldg, w, cols / parts, parts, eps, gate_first);
+  else
+    gated_group_norm_kernel<float><<<grid, 128, 0, st>>>(static_cast<float*>(out), ldo, y, ldy, gate, ldg, w, cols / parts, parts, eps, gate_first);
+  NVLLM_LAUNCH_CHECK("gated_group_norm_kernel");
+  return 0;
+}

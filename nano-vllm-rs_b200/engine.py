@@ -21,7 +21,7 @@ class CConfig(C.Structure):
                 ("vocab_size", i32), ("hidden_size", i32), ("intermediate_size", i32), ("num_hidden_layers", i32),
                 ("num_attention_heads", i32), ("num_key_value_heads", i32), ("head_dim", i32),
                 ("max_position_embeddings", i32), ("tie_word_embeddings", i32), ("qk_norm", i32),
-                ("kv_layout", i32), ("sampling_seed", i32), ("rms_norm_eps", f32), ("reserved_f", f32), ("rope_theta", f64)]
+                ("kv_layout", i32), ("sampling_seed", i32), ("rms_norm_eps", f32), ("recurrent_state", i32), ("rope_theta", f64)]
 
 
 class CSamplingParams(C.Structure):
@@ -37,7 +37,8 @@ class CBatch(C.Structure):
                 ("seq_ids", C.POINTER(i64)), ("input_ids", C.POINTER(i64)), ("positions", C.POINTER(i64)),
                 ("slot_mapping", C.POINTER(i32)), ("cu_seqlens_q", C.POINTER(i32)), ("cu_seqlens_k", C.POINTER(i32)),
                 ("context_lens", C.POINTER(i32)), ("block_tables", C.POINTER(i32)), ("temperatures", C.POINTER(f32)),
-                ("top_k", C.POINTER(i32)), ("top_p", C.POINTER(f32)), ("logit_rows", C.POINTER(i32))]
+                ("top_k", C.POINTER(i32)), ("top_p", C.POINTER(f32)), ("logit_rows", C.POINTER(i32)),
+                ("state_slots", C.POINTER(i32))]
 
 
 class CSchedStats(C.Structure):
@@ -244,6 +245,7 @@ class Batch:
         self.temperatures = arr(cb.temperatures, n, np.float32)
         self.top_k = arr(cb.top_k, n, np.int32)
         self.top_p = arr(cb.top_p, n, np.float32)
+        self.state_slots = arr(cb.state_slots, n, np.int32) if cb.state_slots else None
 
     def seq_lens(self):
         """Tokens of every scheduled sequence (prompt + completion so far): the `n` of the sampler's row seed."""
@@ -366,8 +368,11 @@ class ModelRunner:
         check(lib().nvllm_runner_init_weights(self.h, seed, std))
 
     def load_weight(self, name, bf16_bits):
-        """bf16_bits: uint16 numpy array [rows, cols] (or [n] for norm weights) holding bf16 bit patterns."""
-        a = np.ascontiguousarray(bf16_bits, dtype=np.uint16)
+        """bf16_bits: uint16 numpy array [rows, cols] (or [n] for norm weights) holding bf16 bit patterns; an int32 array for
+        the integer tables of architectures that have them."""
+        a = np.ascontiguousarray(bf16_bits)
+        if a.dtype != np.int32:
+            a = np.ascontiguousarray(a, dtype=np.uint16)
         rows, cols = (1, a.shape[0]) if a.ndim == 1 else a.shape
         check(lib().nvllm_runner_load_weight(self.h, name.encode(), a.ctypes.data, rows, cols))
 

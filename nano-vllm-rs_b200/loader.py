@@ -59,11 +59,11 @@ def to_bf16_bits(dtype, shape, raw):
 
 
 def write_safetensors(path, tensors):
-    """Minimal writer (tests / tooling): tensors = {name: uint16 bf16-bit array | float32 | float16 array}."""
+    """Minimal writer (tests / tooling): tensors = {name: uint16 bf16-bit array | float32 | float16 | int32 array}."""
     header, blobs, off = {}, [], 0
     for name, a in tensors.items():
         a = np.ascontiguousarray(a)
-        dt = {np.dtype(np.uint16): "BF16", np.dtype(np.float32): "F32", np.dtype(np.float16): "F16"}[a.dtype]
+        dt = {np.dtype(np.uint16): "BF16", np.dtype(np.float32): "F32", np.dtype(np.float16): "F16", np.dtype(np.int32): "I32"}[a.dtype]
         raw = a.tobytes()
         header[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + len(raw)]}
         blobs.append(raw)
@@ -85,6 +85,10 @@ class ModelLoader:
         for name, dtype, shape, raw in read_safetensors(path):
             if len(shape) not in (0, 1, 2):
                 raise ValueError(f"{name}: unsupported rank {len(shape)}")
+            if dtype == "I32":     # integer tables (e.g. a token -> experts map) travel as they are
+                self.runner.load_weight(name, np.frombuffer(raw, dtype=np.int32).reshape(shape))
+                n += 1
+                continue
             bits = to_bf16_bits(dtype, shape, raw)
             self.runner.load_weight(name, bits.reshape(1) if bits.ndim == 0 else bits)   # slices + packs on the device side
             n += 1
