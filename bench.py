@@ -53,9 +53,11 @@ def parse():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=None, help="override the workload model (qwen3-0.6b | qwen3-8b | qwen3-32b)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefix", "kosazen"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefix", "kosazen", "talapel"],
                     help="kosazen: prefill / decode throughput and a per-kernel roofline table of the Kosazen architecture "
-                         "(latent attention + mixture of experts) beside Qwen3 models of equal layer sizes, random weights")
+                         "(latent attention + mixture of experts) beside Qwen3 models of equal layer sizes, random weights; "
+                         "talapel: the same for the Talapel architecture (capped attention beside a state-space mixer, retention, "
+                         "table-routed experts)")
     ap.add_argument("--seqs", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the in-run parity checks (profiling runs)")
@@ -720,11 +722,62 @@ def kosazen_config(z):
             "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": mlp} for _ in range(z["layers"])]}
 
 
+# Talapel: one parallel layer (attention beside a state-space mixer, dense feed-forward) and one retention layer with
+# table-routed experts, at widths and head sizes of published hybrid models.  The Qwen3 arm: same width, depth, query / kv heads
+# of 128, and an MLP as wide as the mean of what one Talapel token uses per layer.
+TALAPEL_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, s_heads=64, s_groups=8, s_state=128, s_vdim=64, taps=4, r_heads=16,
+                  r_dim=128, r_vdim=128, dense_ff=8192, experts=64, ff=1408, top=6, layers=2, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, s_heads=128, s_groups=8, s_state=128, s_vdim=64, taps=4, r_heads=32,
+                  r_dim=128, r_vdim=128, dense_ff=12288, experts=32, ff=2048, top=4, layers=2, vocab=32768),
+}
+
+
+def talapel_config(z):
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "softcap": 30.0,
+            "q_temp": {"coef": 0.1, "every": 256}}
+    right = {"heads": z["s_heads"], "groups": z["s_groups"], "state": z["s_state"], "vdim": z["s_vdim"], "conv": z["taps"], "norm_groups": z["s_groups"]}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "dense", "ff": z["dense_ff"]}}
+    ret = {"type": "retention", "mixer": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "rot": {"base": 10000.0, "dims": z["r_dim"]},
+                                          "decay": [1.0 - 2.0 ** (-5 - 3 * i / z["r_heads"]) for i in range(z["r_heads"])]},
+           "mlp": {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}}
+    return {"architecture": "Talapel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [par if i % 2 == 0 else ret for i in range(z["layers"])]}
+
+
 def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
     """Algorithmic work of the named launches of ONE layer at n_tok tokens (context ctx per sequence): {name: (flop, bytes)}."""
     W, H, L = z["width"], z["heads"], ctx
     pairs = n_tok * ((L + 1) / 2 if not decode else L)   # (query, key) pairs per head
     out = {}
+    if arch == "talapel":
+        D, V, G = z["dim"], z["vdim"], z["kv_heads"]
+        a_cols = H * D + G * D + G * V + H * V
+        inner, gn = z["s_heads"] * z["s_vdim"], z["s_groups"] * z["s_state"]
+        s_cols = 2 * inner + 2 * gn + z["s_heads"]
+        rq, rv = z["r_heads"] * z["r_dim"], z["r_heads"] * z["r_vdim"]
+        seqs = n_tok if decode else max(1, n_tok // L)
+        gemm = lambda n, k: (2 * n_tok * n * k, 2 * n * k + n_tok * (2 * k + 4 * n))
+        out["attention q k v g projection"] = gemm(a_cols, W)
+        out["capped_attention"] = (2 * pairs * H * (D + V), (n_tok * L if decode else n_tok) * G * (D + V) * 2 + n_tok * H * (D + 2 * V) * 2)
+        out["attention output projection"] = gemm(W, H * V)
+        out["ssd input projection"] = gemm(s_cols, W)
+        out["ssd output projection"] = gemm(W, inner)
+        # recurrences: 4 flop per state element and token (update + read-out); the state is read and written once per portion
+        out["linear_recurrence (ssd)"] = (4 * n_tok * z["s_heads"] * z["s_state"] * z["s_vdim"],
+                                          n_tok * (2 * gn + 2 * inner) * 4 + seqs * z["s_heads"] * z["s_state"] * z["s_vdim"] * 8)
+        out["linear_recurrence (retention)"] = (4 * n_tok * z["r_heads"] * z["r_dim"] * z["r_vdim"],
+                                                n_tok * (2 * rq + 2 * rv) * 4 + seqs * z["r_heads"] * z["r_dim"] * z["r_vdim"] * 8)
+        out["causal_conv"] = (2 * n_tok * (inner + 2 * gn) * z["taps"], n_tok * (inner + 2 * gn) * 8)
+        out["retention q k v g projection"] = gemm(2 * rq + 2 * rv, W)
+        out["retention output projection"] = gemm(W, rv)
+        out["gate_up projection"] = gemm(2 * z["dense_ff"], W)
+        out["down projection"] = gemm(W, z["dense_ff"])
+        used = min(z["experts"], n_tok * z["top"])
+        out["expert up grouped GEMM"] = (2 * n_tok * z["top"] * W * z["ff"], 2 * used * z["ff"] * W)
+        out["expert down grouped GEMM"] = (2 * n_tok * z["top"] * W * z["ff"], 2 * used * z["ff"] * W)
+        return {k: max(f / (tf * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}
     if arch == "kosazen":
         r, rd, d, vd, E, ff, top, sff = z["kv_rank"], z["rot_dim"], z["dim"], z["vdim"], z["experts"], z["ff"], z["top"], z["shared_ff"]
         out["latent_attention"] = (2 * pairs * H * (2 * r + rd), (n_tok // max(1, L) if not decode else n_tok) * L * (r + rd) * 2 + n_tok * H * (2 * r + rd) * 4)
@@ -736,7 +789,7 @@ def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
         out["shared gate_up projection"] = (2 * n_tok * W * 2 * sff, 2 * 2 * sff * W)
         out["shared down projection"] = (2 * n_tok * W * sff, 2 * sff * W)
     else:
-        D, Hkv, I = 128, z["kv_heads"], z["top"] * z["ff"] + z["shared_ff"]
+        D, Hkv, I = 128, z["kv_heads"], z.get("qwen_mlp", z["top"] * z["ff"] + z.get("shared_ff", 0))
         att = "paged_decode_attention" if decode else "prefill_attention"
         out[att] = (4 * pairs * H * D, (n_tok * L if decode else n_tok) * Hkv * D * 2 * 2)
         out["qkv_proj GEMM"] = (2 * n_tok * W * (H + 2 * Hkv) * D, 2 * W * (H + 2 * Hkv) * D)
@@ -746,27 +799,38 @@ def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
     return {k: max(f / (tf * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}   # roofline microseconds
 
 
-def run_arch_compare(args):
+def run_arch_compare(args, new_arch="kosazen"):
     import torch
     from nano_vllm_rs_b200 import engine as E
     hbm, _ = peaks()
     tf, _ = tensor_peak()
     n_prompts, plen, dec_b = 8, 1024, args.seqs or 64
     rng = __import__("numpy").random.default_rng(0)
-    result = {"workload": "kosazen-vs-qwen3", "data": "synthetic", "dtype": "bf16", "prefill": f"{n_prompts} x {plen} tokens per step",
+    result = {"workload": f"{new_arch}-vs-qwen3", "data": "synthetic", "dtype": "bf16", "prefill": f"{n_prompts} x {plen} tokens per step",
               "decode": f"{dec_b} sequences at context {plen}+", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf}, "sizes": {}}
-    for name, z in ARCH_SIZES.items():
+    sizes = ARCH_SIZES if new_arch == "kosazen" else TALAPEL_SIZES
+    only = os.environ.get("BENCH_ARCH_SIZES")          # e.g. "w2048": a subset of the sizes
+    for name, z in sizes.items():
+        if only and name not in only.split(","):
+            continue
+        if new_arch == "talapel":   # the Qwen3 arm's fields: an MLP as wide as the mean of what one token uses per layer
+            z = dict(z, shared_ff=0)
+            mlp_q = (z["dense_ff"] + z["top"] * z["ff"]) // 2 // 64 * 64
+        else:
+            mlp_q = z["top"] * z["ff"] + z["shared_ff"]
         result["sizes"][name] = {}
-        for arch in ("kosazen", "qwen3"):
+        for arch in (new_arch, "qwen3"):
             progress(f"{name} {arch}: building the engine (random weights)")
             blocks = dec_b * (plen + 256) // 256 + 8
             common = dict(kvcache_block_size=256, num_kvcache_blocks=blocks, max_num_seqs=dec_b,
                           max_num_batched_tokens=n_prompts * plen, max_model_len=plen + 256)
             if arch == "kosazen":
                 cfg = E.Config(model_config=kosazen_config(z), **common)
+            elif arch == "talapel":
+                cfg = E.Config(model_config=talapel_config(z), **common)
             else:
                 cfg = E.Config("qwen3-0.6b", vocab_size=z["vocab"], hidden_size=z["width"], num_hidden_layers=z["layers"],
-                               intermediate_size=z["top"] * z["ff"] + z["shared_ff"], num_attention_heads=z["heads"],
+                               intermediate_size=mlp_q, num_attention_heads=z["heads"],
                                num_key_value_heads=z["kv_heads"], tie_word_embeddings=0, max_position_embeddings=4096, **common)
             eng = E.LLMEngine(cfg, seed=7, std=0.02)
             sp = E.SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + 4, ignore_eos=True)
@@ -801,7 +865,7 @@ def run_arch_compare(args):
             decode_tok_s = dec_b * args.steps / (ms / 1e3)
 
             def table(prof, n_tok, decode):
-                roof = kernel_rooflines(z, arch, n_tok, plen, decode, hbm, tf)
+                roof = kernel_rooflines(dict(z, qwen_mlp=mlp_q), arch, n_tok, plen, decode, hbm, tf)
                 rows = {}
                 for k, (calls, us) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
                     per = us / max(1, calls)
@@ -868,6 +932,10 @@ def main():
     torch.cuda.set_device(local)
     lib = E.lib()
     assert lib.nvllm_device_ok() == 1, "no sm_100 device: the product path has no fallback"
+    if args.workload == "talapel":
+        assert world == 1, "--workload talapel is a one-GPU comparison"
+        print(json.dumps(run_arch_compare(args, "talapel")), flush=True)
+        sys.exit(0)
     if args.workload == "kosazen":
         assert world == 1, "--workload kosazen is a one-GPU comparison"
         print(json.dumps(run_arch_compare(args)), flush=True)

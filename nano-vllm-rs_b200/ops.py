@@ -363,3 +363,117 @@ def moe_combine(expert_out, x, shared_out, topk_idx, topk_w, slot_row, experts):
     check(_ffi.lib().nvllm_moe_combine(_p(out), _p(expert_out), _p(x), _p(shared_out), _p(topk_idx), _p(topk_w), _p(slot_row), n,
                                        hidden, topk_idx.shape[1], experts, _dt(x), _stream()))
     return out
+
+
+# (parallel blocks on an f32 stream, capped attention, recurrent mixers: include/nvllm.h)
+
+
+def residual_layernorm(h, addends=(), bias=None, bias_scale=1.0, weight=None, eps=1e-5, dtype=torch.bfloat16):
+    """h (f32 [n, hidden], in place) += sum of scale * addend (+ bias_scale * bias); returns layer_norm(h) * weight in
+    `dtype` (None without a weight).  addends: up to three (tensor, scale), f32 or bf16."""
+    n, hidden = h.shape
+    out = torch.empty((n, hidden), dtype=dtype, device=h.device) if weight is not None else None
+    a = list(addends) + [(None, 0.0)] * (3 - len(addends))
+    args = []
+    for t, s in a:
+        args += [_p(t), float(s), _dt(t) if t is not None else F32]
+    check(_ffi.lib().nvllm_residual_layernorm(_p(out), _p(h), *args, _p(bias), float(bias_scale), _p(weight), n, hidden, eps,
+                                              BF16 if dtype == torch.bfloat16 else F32, _stream()))
+    return out
+
+
+def concat_cast(a, b, dtype):
+    out = torch.empty((a.shape[0], a.shape[1] + b.shape[1]), dtype=dtype, device=a.device)
+    check(_ffi.lib().nvllm_concat_cast(_p(out), _p(a), _p(b), a.shape[0], a.shape[1], b.shape[1], _dt(out), _stream()))
+    return out
+
+
+def embedding_gather_scaled(table, ids, scale, copy=False):
+    n, hidden = ids.shape[0], table.shape[1]
+    h = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    h2 = torch.empty_like(h) if copy else None
+    check(_ffi.lib().nvllm_embedding_gather_scaled(_p(h), _p(h2), _p(table), _p(ids), n, hidden, table.shape[0], float(scale),
+                                                   _dt(table), _stream()))
+    return (h, h2) if copy else h
+
+
+def ff_activation(x, kind):
+    """kind 0: silu(x[:, :ff]) * x[:, ff:];  kind 1: relu(x)^2."""
+    n, cols = x.shape
+    ff = cols // 2 if kind == 0 else cols
+    out = torch.empty((n, ff), dtype=x.dtype, device=x.device)
+    check(_ffi.lib().nvllm_ff_activation(_p(out), _p(x), n, ff, kind, _dt(x), _stream()))
+    return out
+
+
+def moe_table_route(table, ids):
+    n, top = ids.shape[0], table.shape[1]
+    idx = torch.empty((n, top), dtype=torch.int32, device=ids.device)
+    w = torch.empty((n, top), dtype=torch.float32, device=ids.device)
+    check(_ffi.lib().nvllm_moe_table_route(_p(idx), _p(w), _p(table), _p(ids), n, top, table.shape[0], _stream()))
+    return idx, w
+
+
+def attn_bias_store(proj, q_cols, k_cols, v_cols, q_bias, k_bias, v_bias, k_cache, v_cache, slots, dtype):
+    """proj: f32 [n, >= q + k + v columns].  Returns q in `dtype`; k / v (+ biases) go to cache rows `slots`."""
+    n = proj.shape[0]
+    q = torch.empty((n, q_cols), dtype=dtype, device=proj.device)
+    check(_ffi.lib().nvllm_attn_bias_store(_p(q), q.stride(0), _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(proj),
+                                           proj.stride(0), _p(q_bias), _p(k_bias), _p(v_bias), _p(slots), n, q_cols, k_cols, v_cols,
+                                           _dt(q), _stream()))
+    return q
+
+
+def capped_attention(q, gate, k_cache, v_cache, tok_seq, positions, tables, block_size, heads, kv_heads, dim, vdim, scale,
+                     softcap=0.0, temp_coef=0.0, temp_every=1):
+    n = q.shape[0]
+    out = torch.empty((n, heads * vdim), dtype=q.dtype, device=q.device)
+    check(_ffi.lib().nvllm_capped_attention(_p(out), out.stride(0), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
+                                            _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(tok_seq), _p(positions),
+                                            _p(tables), tables.shape[1], block_size, n, heads, kv_heads, dim, vdim, scale, softcap,
+                                            temp_coef, temp_every, _dt(q), _stream()))
+    return out
+
+
+def linear_recurrence(q, k, v, decay, state, seq_slot, cu_tokens, positions, heads, groups, dk, dv, step=None, skip=None):
+    """S <- a S + b k v^T, y = S^T q + skip * v over the sequences of a step; state [slots, heads, dk, dv] f32 is updated.
+    decay / step: [n, heads] (per token) or [heads]."""
+    n = v.shape[0]
+    y = torch.empty((n, heads * dv), dtype=torch.float32, device=v.device)
+    check(_ffi.lib().nvllm_linear_recurrence(_p(y), y.stride(0), _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(decay),
+                                             int(decay.dim() == 2), _p(step), int(step is not None and step.dim() == 2), _p(skip),
+                                             _p(state), _p(seq_slot), _p(cu_tokens), _p(positions), seq_slot.shape[0], heads, groups, dk,
+                                             dv, _stream()))
+    return y
+
+
+def causal_conv(x, w, bias, state, tok_seq, seq_slot, cu_tokens, positions, silu=True):
+    """x f32 [n, channels] (a view with a row stride is fine), w [channels, taps], state [slots, taps - 1, channels] (updated)."""
+    n, ch = x.shape
+    out = torch.empty((n, ch), dtype=torch.float32, device=x.device)
+    check(_ffi.lib().nvllm_causal_conv(_p(out), out.stride(0), _p(x), x.stride(0), _p(w), _p(bias), _p(state), _p(tok_seq), _p(seq_slot),
+                                       _p(cu_tokens), _p(positions), n, seq_slot.shape[0], ch, w.shape[1], int(silu), _stream()))
+    return out
+
+
+def ssd_prepare(dt_raw, dt_bias, a_log):
+    n, heads = dt_raw.shape
+    step = torch.empty((n, heads), dtype=torch.float32, device=dt_raw.device)
+    decay = torch.empty_like(step)
+    check(_ffi.lib().nvllm_ssd_prepare(_p(step), _p(decay), _p(dt_raw), dt_raw.stride(0), _p(dt_bias), _p(a_log), n, heads, _stream()))
+    return step, decay
+
+
+def rotate_half(x, positions, table, heads, dim, dims, scale=1.0):
+    """In place on f32 x [n, heads * dim] (row stride allowed)."""
+    check(_ffi.lib().nvllm_rotate_half(_p(x), x.stride(0), _p(positions), _p(table), table.shape[0] if table is not None else 1,
+                                       x.shape[0], heads, dim, dims, float(scale), _stream()))
+    return x
+
+
+def gated_group_norm(y, gate, weight, parts, eps, gate_first, dtype):
+    n, cols = y.shape
+    out = torch.empty((n, cols), dtype=dtype, device=y.device)
+    check(_ffi.lib().nvllm_gated_group_norm(_p(out), out.stride(0), _p(y), y.stride(0), _p(gate), gate.stride(0), _p(weight), n, cols,
+                                            parts, eps, int(gate_first), _dt(out), _stream()))
+    return out

@@ -29,6 +29,14 @@ def bf16_round(a):
     return u.view(np.float32).astype(np.float64)
 
 
+def to_bf16_bits(a):
+    """bf16-representable float values -> uint16 bit patterns (integer arrays pass as int32)."""
+    a = np.asarray(a)
+    if a.dtype.kind in "iu":
+        return a.astype(np.int32)
+    return (np.ascontiguousarray(a, np.float32).view(np.uint32) >> np.uint32(16)).astype(np.uint16)
+
+
 # ---- configuration / weights --------------------------------------------------------------------------------------------
 def parallel_mixer(heads=4, kv_heads=2, dim=6, vdim=10, scale=0.3, softcap=8.0, coef=0.4, every=3, s_heads=3, groups=1,
                    state=5, s_vdim=4, taps=3, norm_groups=1, left_scale=0.9, right_scale=1.3):
@@ -180,7 +188,8 @@ def capped_attention_token(h, w, p, m, pos, rows):
     for hh in range(H):
         g = hh // (H // G)
         s = np.array([q[hh] @ k[g] for k, _ in rows]) * m["scale"]
-        s = m["softcap"] * np.tanh(s / m["softcap"])
+        if m.get("softcap", 0.0) > 0.0:
+            s = m["softcap"] * np.tanh(s / m["softcap"])
         e = np.exp(s - s.max())
         e /= e.sum()
         out[hh] = sum(pj * v[g] for pj, (_, v) in zip(e, rows))
@@ -220,6 +229,8 @@ def rotate_half(v, pos, dims, base):
     """Rotary position on the first `dims` values of every row of v (rows = heads): dimension i pairs with i + dims/2."""
     out = v.copy()
     half = dims // 2
+    if half == 0:
+        return out
     ang = pos * base ** (-2.0 * np.arange(half) / dims)
     a, b = v[:, :half], v[:, half:dims]
     out[:, :half] = a * np.cos(ang) - b * np.sin(ang)
