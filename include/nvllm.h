@@ -446,13 +446,15 @@ int nvllm_attn_bias_store(void* q, int64_t ldq, void* k_cache, void* v_cache, in
  *   s[t, h, j] = cap(scale * temp(p_t) * q[t, h] . k[j, h / (heads / kv_heads)]),  j <= p_t = positions[t] in sequence tok_seq[t]
  *   temp(p) = 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1),  cap(s) = softcap * tanh(s / softcap) (softcap <= 0: s)
  *   out[t, h, :] = sum_j softmax_j(s) v[j, ...] * sigmoid(gate[t, h, :])   (gate: f32, nullable)
- * Key size dim, value size vdim (<= 256).  block_tables: [sequences, table_cap]. */
+ * Key size dim, value size vdim (<= 256).  block_tables: [sequences, table_cap].  cu_tokens (nullable): [n_seqs + 1] token
+ * range of every sequence in the batch, tokens in order of position; with it, bf16 problems whose rows are 16-byte multiples
+ * (dim, vdim <= 128) run on tensor cores, 64 (token, head) rows of one sequence and key / value head per CTA. */
 int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
                            const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
                            const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
                            int32_t table_cap, int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
-                           int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every, int32_t dtype,
-                           void* stream);
+                           int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every,
+                           const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream);
 
 /* Recurrent mixers.  A step lists its sequences: seq_slot[s] = the state slot of sequence s (< 0: padding, output zero),
  * cu_tokens[s] .. cu_tokens[s + 1] = its tokens in the batch (in order of position), positions[] per token.  A portion

@@ -84,7 +84,7 @@ PROTOTYPES = {
     "nvllm_moe_table_route": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
     "nvllm_attn_bias_store": (i32, [vp, i64, vp, vp, i64, i64, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "nvllm_capped_attention": (i32, [vp, i64, vp, i64, vp, i64, vp, vp, i64, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
-                                     f32, f32, f32, i32, i32, vp]),
+                                     f32, f32, f32, i32, vp, i32, i32, vp]),
     "nvllm_linear_recurrence": (i32, [vp, i64, vp, i64, vp, i64, vp, i64, vp, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32,
                                       i32, vp]),
     "nvllm_causal_conv": (i32, [vp, i64, vp, i64, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]),

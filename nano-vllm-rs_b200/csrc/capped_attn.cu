@@ -122,6 +122,187 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
   }
 }
 
+
+// ---- tensor cores (bf16) ------------------------------------------------------------------------------------------
+// CTA = 64 rows x one key/value head; a row is a (token, query head of the group) pair, so the heads that share a key /
+// value head and up to 64 / group tokens of ONE sequence read every key tile once: whole prompts fill the M dimension with
+// tokens, single decoded tokens with the heads of the group.  4 warps x 16 rows; key tiles of 64 through the block table,
+// double-buffered with cp.async; S = Q.K^T and O += P.V on mma.sync m16n8k16 (P stays in registers); scale, temperature,
+// cap, mask and the online softmax in f32.  Key tiles start at multiples of 64 from the sequence's first key whatever the
+// portion, so a row's result does not depend on how the prompt was cut.  Head sizes are padded to DMAX / VMAX with zeros in
+// shared memory.
+constexpr int kRows = 64, kKeys = 64;
+
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - 2.0f / (__expf(2.0f * x) + 1.0f); }
+
+template <int DMAX, int VMAX>
+__global__ void __launch_bounds__(128) capped_attn_mma_kernel(const AttnArgs a, const int32_t* __restrict__ cu_tokens, int n_seqs, int tq,
+                                                              int group) {
+  constexpr int QS = DMAX + 8, VS = VMAX + 8;       // shared-memory row strides (elements): 16-byte rows, conflict-free ldmatrix
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [64][QS]
+  bf16* Ks = Qs + kRows * QS;                        // [2][64][QS]
+  bf16* Vs = Ks + 2 * kKeys * QS;                    // [2][64][VS]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq4 = lane & 3;
+  const int g = blockIdx.y;
+  // which (sequence, token tile) is this CTA's
+  int tile = blockIdx.x, seq = -1, tok0 = 0, ntok = 0;
+  for (int s = 0; s < n_seqs; ++s) {
+    const int c0 = cu_tokens[s], len = cu_tokens[s + 1] - c0, nt = (len + tq - 1) / tq;
+    if (tile < nt) { seq = s; tok0 = c0 + tile * tq; ntok = min(tq, len - tile * tq); break; }
+    tile -= nt;
+  }
+  if (seq < 0) return;
+  const int nkeys = static_cast<int>(a.positions[tok0 + ntok - 1]) + 1;   // tokens of a sequence are in order of position
+  const int32_t* table = a.tables + static_cast<int64_t>(seq) * a.table_cap;
+  const bf16* qg = static_cast<const bf16*>(a.q);
+  const bf16* kc = static_cast<const bf16*>(a.kc) + static_cast<int64_t>(g) * a.dim;
+  const bf16* vc = static_cast<const bf16*>(a.vc) + static_cast<int64_t>(g) * a.vdim;
+  // zero everything once (padding columns and rows stay zero), then the query rows
+  for (int i = tid; i < (kRows * QS + 2 * kKeys * QS + 2 * kKeys * VS) / 8; i += 128) reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  const int dch = a.dim / 8, vch = a.vdim / 8;     // 16-byte chunks per row
+  for (int i = tid; i < kRows * dch; i += 128) {
+    const int r = i / dch, c = i % dch, t = r / group, hr = r % group;
+    if (t < ntok)
+      *reinterpret_cast<uint4*>(Qs + r * QS + c * 8) =
+          *reinterpret_cast<const uint4*>(qg + static_cast<int64_t>(tok0 + t) * a.ldq + static_cast<int64_t>(g * group + hr) * a.dim + c * 8);
+  }
+  auto load_tile = [&](int kt, int buf) {
+    bf16* kd = Ks + buf * kKeys * QS;
+    bf16* vd = Vs + buf * kKeys * VS;
+    for (int i = tid; i < kKeys * (dch + vch); i += 128) {
+      const int r = i / (dch + vch), c = i % (dch + vch), j = kt * kKeys + r;
+      int64_t slot = -1;
+      if (j < nkeys) {
+        const int32_t blk = table[j / a.block_size];
+        if (blk >= 0) slot = static_cast<int64_t>(blk) * a.block_size + j % a.block_size;
+      }
+      if (c < dch) cp_async_16(smem_u32(kd + r * QS + c * 8), slot >= 0 ? kc + slot * a.k_row + c * 8 : kc, slot >= 0 ? 16 : 0);
+      else cp_async_16(smem_u32(vd + r * VS + (c - dch) * 8), slot >= 0 ? vc + slot * a.v_row + (c - dch) * 8 : vc, slot >= 0 ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+  // this thread's two rows
+  int pos[2]; float qscale[2]; bool valid[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = warp * 16 + gq + 8 * i, t = r / group;
+    valid[i] = t < ntok && r < tq * group;
+    pos[i] = valid[i] ? static_cast<int>(a.positions[tok0 + t]) : -1;
+    qscale[i] = a.scale * (1.0f + a.temp_coef * logf(floorf(static_cast<float>((pos[i] + 1) / a.temp_every)) + 1.0f));
+  }
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[VMAX / 8][4];
+#pragma unroll
+  for (int i = 0; i < VMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
+  const int ntiles = (nkeys + kKeys - 1) / kKeys;
+  load_tile(0, 0);
+  const uint32_t q_addr = smem_u32(Qs + (warp * 16 + (lane & 15)) * QS + (lane >> 4) * 8);
+  for (int kt = 0; kt < ntiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < ntiles) { load_tile(kt + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const bf16* kb = Ks + buf * kKeys * QS;
+    const bf16* vb = Vs + buf * kKeys * VS;
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    const uint32_t k_addr = smem_u32(kb + ((lane & 7) + (lane >> 4) * 8) * QS + ((lane >> 3) & 1) * 8);
+#pragma unroll
+    for (int kk = 0; kk < DMAX / 16; ++kk) {
+      uint32_t af[4];
+      ldmatrix_x4(af, q_addr + kk * 32);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t bk[4];
+        ldmatrix_x4(bk, k_addr + np * 16 * QS * 2 + kk * 32);
+        mma_bf16_16816(s[2 * np], af, bk[0], bk[1]);
+        mma_bf16_16816(s[2 * np + 1], af, bk[2], bk[3]);
+      }
+    }
+    // scale, temperature, cap, causal mask; online softmax per row
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1, j = kt * kKeys + nt * 8 + 2 * tq4 + (e & 1);
+        float v = s[nt][e] * qscale[i];
+        if (a.softcap > 0.f) v = a.softcap * fast_tanh(v * inv_cap);
+        v = j <= pos[i] ? v : -INFINITY;
+        s[nt][e] = v;
+        mx[i] = fmaxf(mx[i], v);
+      }
+    float corr[2], mu[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float mn = fmaxf(m[i], mx[i]);
+      mu[i] = mn == -INFINITY ? 0.f : mn;
+      corr[i] = __expf(m[i] - mu[i]);
+      m[i] = mn;
+      l[i] *= corr[i];
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = __expf(s[nt][e] - mu[e >> 1]);
+        s[nt][e] = p;
+        l[e >> 1] += p;
+      }
+#pragma unroll
+    for (int i = 0; i < VMAX / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+    const uint32_t v_addr = smem_u32(vb + ((lane & 7) + ((lane >> 3) & 1) * 8) * VS + (lane >> 4) * 8);
+#pragma unroll
+    for (int kc2 = 0; kc2 < 4; ++kc2) {
+      uint32_t pf[4];
+      pf[0] = pack_bf16x2(s[2 * kc2][0], s[2 * kc2][1]); pf[1] = pack_bf16x2(s[2 * kc2][2], s[2 * kc2][3]);
+      pf[2] = pack_bf16x2(s[2 * kc2 + 1][0], s[2 * kc2 + 1][1]); pf[3] = pack_bf16x2(s[2 * kc2 + 1][2], s[2 * kc2 + 1][3]);
+#pragma unroll
+      for (int vp = 0; vp < VMAX / 16; ++vp) {
+        uint32_t bv[4];
+        ldmatrix_x4_trans(bv, v_addr + kc2 * 16 * VS * 2 + vp * 32);
+        mma_bf16_16816(o[2 * vp], pf, bv[0], bv[1]);
+        mma_bf16_16816(o[2 * vp + 1], pf, bv[2], bv[3]);
+      }
+    }
+    __syncthreads();   // everyone is done with this buffer before the next load overwrites it
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    if (!valid[i]) continue;
+    const int r = warp * 16 + gq + 8 * i, t = r / group, h = g * group + r % group;
+    const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    bf16* op = static_cast<bf16*>(a.out) + static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim;
+    const float* gt = a.gate ? a.gate + static_cast<int64_t>(tok0 + t) * a.ldg + static_cast<int64_t>(h) * a.vdim : nullptr;
+#pragma unroll
+    for (int vt = 0; vt < VMAX / 8; ++vt) {
+      const int c = vt * 8 + 2 * tq4;
+      if (c >= a.vdim) continue;
+      float v0 = o[vt][2 * i] * inv, v1 = o[vt][2 * i + 1] * inv;
+      if (gt) { v0 *= 1.0f / (1.0f + __expf(-gt[c])); v1 *= 1.0f / (1.0f + __expf(-gt[c + 1])); }
+      *reinterpret_cast<uint32_t*>(op + c) = pack_bf16x2(v0, v1);
+    }
+  }
+}
+
+template <int DMAX, int VMAX>
+int launch_mma(const AttnArgs& a, const int32_t* cu_tokens, int n_seqs, cudaStream_t st) {
+  const int group = a.heads / a.kv_heads, tq = kRows / group;
+  const size_t smem = (static_cast<size_t>(kRows) * (DMAX + 8) + 2 * kKeys * (DMAX + 8) + 2 * kKeys * (VMAX + 8)) * sizeof(bf16);
+  NVLLM_SMEM_ATTR_ONCE((capped_attn_mma_kernel<DMAX, VMAX>), smem);
+  dim3 grid((a.n + tq - 1) / tq + n_seqs, a.kv_heads);
+  capped_attn_mma_kernel<DMAX, VMAX><<<grid, 128, smem, st>>>(a, cu_tokens, n_seqs, tq, group);
+  NVLLM_LAUNCH_CHECK("capped_attn_mma_kernel");
+  return 0;
+}
+
 }  // namespace
 }  // namespace nvllm
 
@@ -151,8 +332,8 @@ extern "C" int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int
                                       const void* k_cache, const void* v_cache, int64_t k_row, int64_t v_row,
                                       const int32_t* tok_seq, const int64_t* positions, const int32_t* block_tables,
                                       int32_t table_cap, int32_t block_size, int32_t n, int32_t heads, int32_t kv_heads, int32_t dim,
-                                      int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every, int32_t dtype,
-                                      void* stream) {
+                                      int32_t vdim, float scale, float softcap, float temp_coef, int32_t temp_every,
+                                      const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream) {
   NVLLM_CHECK_ARG(n >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && vdim <= 32 * kMaxVPerLane &&
                       dim <= 2048 && block_size > 0 && table_cap > 0 && temp_every > 0, NVLLM_ERR_ARG,
                   "capped_attention: n=%d heads=%d/%d dim=%d vdim=%d (vdim <= 256)", n, heads, kv_heads, dim, vdim);
@@ -162,6 +343,14 @@ extern "C" int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int
   AttnArgs a{out, ldo, q, ldq, gate, ldg, k_cache, v_cache, k_row, v_row, tok_seq, positions, block_tables, table_cap, block_size,
              n, heads, kv_heads, dim, vdim, scale, softcap, temp_coef, temp_every};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // bf16 with 16-byte rows and a token range per sequence: tensor cores; everything else (f32, odd sizes): one warp per row
+  const int group = heads / kv_heads;
+  if (dtype == NVLLM_BF16 && cu_tokens != nullptr && n_seqs > 0 && knobs().capped_mma && group <= kRows && dim % 8 == 0 && vdim % 8 == 0 &&
+      dim <= 128 && vdim <= 128 && ldq % 8 == 0 && k_row % 8 == 0 && v_row % 8 == 0 && ldo % 2 == 0 && aligned16(q) && aligned16(k_cache) &&
+      aligned16(v_cache) && (reinterpret_cast<uintptr_t>(out) & 3u) == 0) {
+    if (dim <= 64 && vdim <= 64) return launch_mma<64, 64>(a, cu_tokens, n_seqs, st);
+    return launch_mma<128, 128>(a, cu_tokens, n_seqs, st);
+  }
   const unsigned grid = static_cast<unsigned>((static_cast<int64_t>(n) * heads + 3) / 4);
   const size_t smem = static_cast<size_t>(4) * dim * sizeof(float);
   if (dtype == NVLLM_BF16) capped_attn_warp_kernel<bf16><<<grid, 128, smem, st>>>(a);

@@ -525,7 +525,7 @@ class Talapel : public ModelImpl {
         RUN(lin(proj_, normed_, L.a_in, lda, W, lda, NVLLM_F32, "attention q k v g projection"));
         RUN(nvllm_attn_bias_store(q_, qn, rs.kc, rs.vc, kn, vn, proj_, lda, L.qb, L.kb, L.vb, v.slots, N, qn, kn, vn, dt_, st)); ++launches; mk("attn_bias_store");
         RUN(nvllm_capped_attention(mix_in_, gn, q_, qn, proj_ + qn + kn + vn, lda, rs.kc, rs.vc, kn, vn, v.tok_seq, v.positions, v.tables,
-                                   v.table_cap, lim_.block_size, N, L.H, L.G, L.D, L.V, L.scale, L.softcap, L.temp_coef, L.temp_every, dt_, st)); ++launches; mk("capped_attention");
+                                   v.table_cap, lim_.block_size, N, L.H, L.G, L.D, L.V, L.scale, L.softcap, L.temp_coef, L.temp_every, v.cu_tokens, S, dt_, st)); ++launches; mk("capped_attention");
         RUN(lin(left_out_, mix_in_, L.a_o, W, gn, W, NVLLM_F32, "attention output projection"));
         // --- ssd: [z | x | B | C | dt] in one projection, convolution + SiLU over (x, B, C), recurrence, gated norm, Wo
         const int inner = L.s_inner(), gns = L.sG * L.sN, ch = L.s_ch(), lds = pad8(L.s_cols());

@@ -425,13 +425,14 @@ def attn_bias_store(proj, q_cols, k_cols, v_cols, q_bias, k_bias, v_bias, k_cach
 
 
 def capped_attention(q, gate, k_cache, v_cache, tok_seq, positions, tables, block_size, heads, kv_heads, dim, vdim, scale,
-                     softcap=0.0, temp_coef=0.0, temp_every=1):
+                     softcap=0.0, temp_coef=0.0, temp_every=1, cu_tokens=None):
     n = q.shape[0]
     out = torch.empty((n, heads * vdim), dtype=q.dtype, device=q.device)
     check(_ffi.lib().nvllm_capped_attention(_p(out), out.stride(0), _p(q), q.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                             _p(k_cache), _p(v_cache), k_cache.stride(0), v_cache.stride(0), _p(tok_seq), _p(positions),
                                             _p(tables), tables.shape[1], block_size, n, heads, kv_heads, dim, vdim, scale, softcap,
-                                            temp_coef, temp_every, _dt(q), _stream()))
+                                            temp_coef, temp_every, _p(cu_tokens), cu_tokens.shape[0] - 1 if cu_tokens is not None else 0,
+                                            _dt(q), _stream()))
     return out
 
 

@@ -124,10 +124,11 @@ def _attention_ref(q, keys, vals, m, pos):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,V", [(4, 2, 6, 10), (3, 3, 16, 16), (5, 1, 40, 33)])
+@pytest.mark.parametrize("H,G,D,V", [(4, 2, 6, 10), (3, 3, 16, 16), (5, 1, 40, 33), (8, 2, 48, 96), (6, 2, 64, 32), (2, 1, 128, 128)])
 def test_capped_attention_paged(cuda, dtype, H, G, D, V):
     """Prompt portions and single tokens of three sequences in one launch, pages in random order, query positions around the
-    temperature steps and the page borders; biases, the gate and the cache store included."""
+    temperature steps and the page borders; biases, the gate and the cache store included.  bf16 with head sizes that are
+    multiples of 8 runs on the tensor-core kernel (groups of 1, 3, 4 and 2 heads per key head), the rest one warp per row."""
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(H * 100 + D)
     bs, every = 8, 5
@@ -137,7 +138,7 @@ def test_capped_attention_paged(cuda, dtype, H, G, D, V):
     tables, slot, nslots = _paged(rng, ctx, bs)
     rd = lambda *s: T.bf16_round(rng.standard_normal(s)) if dtype == torch.bfloat16 else rng.standard_normal(s)
     K = [rd(c, G, D) for c in ctx]; Vv = [rd(c, G, V) for c in ctx]
-    kc = torch.zeros((nslots, G * D + 3), dtype=dtype, device=cuda); vc = torch.zeros((nslots, G * V), dtype=dtype, device=cuda)
+    kc = torch.zeros((nslots, G * D + 8), dtype=dtype, device=cuda); vc = torch.zeros((nslots, G * V), dtype=dtype, device=cuda)
     qb, kb, vb = rng.standard_normal(H * D), rng.standard_normal(G * D), rng.standard_normal(G * V)
     proj, slots, tok_seq, pos = [], [], [], []
     for s, (c, n) in enumerate(zip(ctx, new)):
@@ -152,7 +153,11 @@ def test_capped_attention_paged(cuda, dtype, H, G, D, V):
     qd = ops.attn_bias_store(pd, H * D, G * D, G * V, dev_t(qb, cuda), dev_t(kb, cuda), dev_t(vb, cuda), kc, vc, dev_i(slots, cuda), dtype)
     gate = pd[:, H * D + G * D + G * V:]
     out = ops.capped_attention(qd, gate, kc, vc, dev_i(tok_seq, cuda), dev_i(pos, cuda, torch.int64), dev_i(tables, cuda), bs, H, G, D, V,
-                               m["scale"], m["softcap"], 0.6, every).float().cpu().numpy()
+                               m["scale"], m["softcap"], 0.6, every, cu_tokens=dev_i(np.concatenate([[0], np.cumsum(new)]), cuda)).float().cpu().numpy()
+    if dtype == torch.bfloat16:   # the kernel without the token ranges (one warp per row) agrees with the tensor-core one
+        plain = ops.capped_attention(qd, gate, kc, vc, dev_i(tok_seq, cuda), dev_i(pos, cuda, torch.int64), dev_i(tables, cuda), bs, H, G, D, V,
+                                     m["scale"], m["softcap"], 0.6, every).float().cpu().numpy()
+        np.testing.assert_allclose(out, plain, rtol=2e-2, atol=2e-2)
     qs = qd.float().cpu().numpy().astype(np.float64)
     tol = 2e-2 if dtype == torch.bfloat16 else 2e-5
     for i, (s, p) in enumerate(zip(tok_seq, pos)):
@@ -173,7 +178,7 @@ def test_capped_attention_one_key_stands_out(cuda, where, dtype):
     unless it lies in the future (`next`)."""
     from nano_vllm_rs_b200 import ops
     rng = np.random.default_rng(7)
-    H, G, D, V, bs, ctx = 2, 1, 16, 12, 16, 300
+    H, G, D, V, bs, ctx = 2, 1, 16, 16, 16, 300
     qpos = 250
     at = {"first": 0, "far": 37, "page_end": 16 * 9 + 15, "page_start": 16 * 10, "last": qpos, "next": qpos + 1}[where]
     tables, slot, nslots = _paged(rng, [ctx], bs)
@@ -184,7 +189,8 @@ def test_capped_attention_one_key_stands_out(cuda, where, dtype):
     for p in range(ctx):
         kc[slot(0, p)] = dev_t(K[p], cuda, dtype); vc[slot(0, p)] = dev_t(Vv[p], cuda, dtype)
     out = ops.capped_attention(dev_t(q.reshape(1, -1), cuda, dtype), None, kc, vc, dev_i([0], cuda), dev_i([qpos], cuda, torch.int64),
-                               dev_i(tables, cuda), bs, H, G, D, V, 1.0, 20.0, 0.0, 1).float().cpu().numpy().reshape(H, V)
+                               dev_i(tables, cuda), bs, H, G, D, V, 1.0, 20.0, 0.0, 1,
+                               cu_tokens=dev_i([0, 1], cuda)).float().cpu().numpy().reshape(H, V)   # bf16: tensor cores
     m = {"heads": H, "kv_heads": G, "dim": D, "vdim": V, "scale": 1.0, "softcap": 20.0, "q_temp": {"coef": 0.0, "every": 1}}
     ref = _attention_ref(q, [k[None] for k in K[:qpos + 1]], [v[None] for v in Vv[:qpos + 1]], m, qpos)
     np.testing.assert_allclose(out, ref, rtol=2e-2, atol=2e-2)
