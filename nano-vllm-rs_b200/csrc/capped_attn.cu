@@ -124,19 +124,20 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
 
 
 // ---- tensor cores (bf16) ------------------------------------------------------------------------------------------
-// CTA = 64 rows x one key/value head; a row is a (token, query head of the group) pair, so the heads that share a key /
-// value head and up to 64 / group tokens of ONE sequence read every key tile once: whole prompts fill the M dimension with
-// tokens, single decoded tokens with the heads of the group.  4 warps x 16 rows; key tiles of 64 through the block table,
+// CTA = 128 rows x one key/value head; a row is a (token, query head of the group) pair, so the heads that share a key /
+// value head and up to 128 / group tokens of ONE sequence read every key tile once: whole prompts fill the M dimension with
+// tokens, single decoded tokens with the heads of the group (warps whose 16 rows are all empty only help with the copies).
+// 8 warps x 16 rows; key tiles of 64 through the block table,
 // double-buffered with cp.async; S = Q.K^T and O += P.V on mma.sync m16n8k16 (P stays in registers); scale, temperature,
 // cap, mask and the online softmax in f32.  Key tiles start at multiples of 64 from the sequence's first key whatever the
 // portion, so a row's result does not depend on how the prompt was cut.  Head sizes are padded to DMAX / VMAX with zeros in
 // shared memory.
-constexpr int kRows = 64, kKeys = 64;
+constexpr int kWarps = 8, kRows = 16 * kWarps, kKeys = 64, kThreads = 32 * kWarps;
 
-__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - 2.0f / (__expf(2.0f * x) + 1.0f); }
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
 
 template <int DMAX, int VMAX>
-__global__ void __launch_bounds__(128) capped_attn_mma_kernel(const AttnArgs a, const int32_t* __restrict__ cu_tokens, int n_seqs, int tq,
+__global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const AttnArgs a, const int32_t* __restrict__ cu_tokens, int n_seqs, int tq,
                                                               int group) {
   constexpr int QS = DMAX + 8, VS = VMAX + 8;       // shared-memory row strides (elements): 16-byte rows, conflict-free ldmatrix
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -159,28 +160,35 @@ __global__ void __launch_bounds__(128) capped_attn_mma_kernel(const AttnArgs a, 
   const bf16* kc = static_cast<const bf16*>(a.kc) + static_cast<int64_t>(g) * a.dim;
   const bf16* vc = static_cast<const bf16*>(a.vc) + static_cast<int64_t>(g) * a.vdim;
   // zero everything once (padding columns and rows stay zero), then the query rows
-  for (int i = tid; i < (kRows * QS + 2 * kKeys * QS + 2 * kKeys * VS) / 8; i += 128) reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < (kRows * QS + 2 * kKeys * QS + 2 * kKeys * VS) / 8; i += kThreads) reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   const int dch = a.dim / 8, vch = a.vdim / 8;     // 16-byte chunks per row
-  for (int i = tid; i < kRows * dch; i += 128) {
+  for (int i = tid; i < kRows * dch; i += kThreads) {
     const int r = i / dch, c = i % dch, t = r / group, hr = r % group;
     if (t < ntok)
       *reinterpret_cast<uint4*>(Qs + r * QS + c * 8) =
           *reinterpret_cast<const uint4*>(qg + static_cast<int64_t>(tok0 + t) * a.ldq + static_cast<int64_t>(g * group + hr) * a.dim + c * 8);
   }
+  // Cache slot of every key of a tile: looked up by 64 threads one tile ahead of the copy that needs it (the table read is a
+  // dependent global load; in the copy loop it would serialise), kept in shared memory [2][64].
+  __shared__ int64_t slot_s[2][kKeys];
+  auto lookup = [&](int kt) -> int64_t {          // threads 0..63: key kt * 64 + tid
+    const int j = kt * kKeys + tid;
+    if (j >= nkeys) return -1;
+    const int32_t blk = table[j / a.block_size];
+    return blk >= 0 ? static_cast<int64_t>(blk) * a.block_size + j % a.block_size : -1;
+  };
+  // thread -> (key row, every fourth 16-byte chunk of it): no index arithmetic in the copy loop
+  const int lr = tid >> 2, lh = tid & 3;
   auto load_tile = [&](int kt, int buf) {
-    bf16* kd = Ks + buf * kKeys * QS;
-    bf16* vd = Vs + buf * kKeys * VS;
-    for (int i = tid; i < kKeys * (dch + vch); i += 128) {
-      const int r = i / (dch + vch), c = i % (dch + vch), j = kt * kKeys + r;
-      int64_t slot = -1;
-      if (j < nkeys) {
-        const int32_t blk = table[j / a.block_size];
-        if (blk >= 0) slot = static_cast<int64_t>(blk) * a.block_size + j % a.block_size;
-      }
-      if (c < dch) cp_async_16(smem_u32(kd + r * QS + c * 8), slot >= 0 ? kc + slot * a.k_row + c * 8 : kc, slot >= 0 ? 16 : 0);
-      else cp_async_16(smem_u32(vd + r * VS + (c - dch) * 8), slot >= 0 ? vc + slot * a.v_row + (c - dch) * 8 : vc, slot >= 0 ? 16 : 0);
-    }
+    bf16* kd = Ks + buf * kKeys * QS + lr * QS;
+    bf16* vd = Vs + buf * kKeys * VS + lr * VS;
+    const int64_t slot = slot_s[kt & 1][lr];
+    const bf16* ksrc = slot >= 0 ? kc + slot * a.k_row : kc;
+    const bf16* vsrc = slot >= 0 ? vc + slot * a.v_row : vc;
+    const int nb = slot >= 0 ? 16 : 0;
+    for (int c = lh; c < dch; c += 4) cp_async_16(smem_u32(kd + c * 8), ksrc + (nb ? c * 8 : 0), nb);
+    for (int c = lh; c < vch; c += 4) cp_async_16(smem_u32(vd + c * 8), vsrc + (nb ? c * 8 : 0), nb);
     cp_async_commit();
   };
   // this thread's two rows
@@ -192,18 +200,26 @@ __global__ void __launch_bounds__(128) capped_attn_mma_kernel(const AttnArgs a, 
     pos[i] = valid[i] ? static_cast<int>(a.positions[tok0 + t]) : -1;
     qscale[i] = a.scale * (1.0f + a.temp_coef * logf(floorf(static_cast<float>((pos[i] + 1) / a.temp_every)) + 1.0f));
   }
+  // rows of a warp: 16 consecutive (token, head) pairs; the first decides whether the warp has any, the smallest position
+  // whether a tile needs the causal mask (empty rows count as hidden)
+  const bool warp_has_rows = (warp * 16) / group < ntok;
+  const int min_pos = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[VMAX / 8][4];
 #pragma unroll
   for (int i = 0; i < VMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
   const int ntiles = (nkeys + kKeys - 1) / kKeys;
+  if (tid < kKeys) { slot_s[0][tid] = lookup(0); slot_s[1][tid] = lookup(1); }
+  __syncthreads();
   load_tile(0, 0);
   const uint32_t q_addr = smem_u32(Qs + (warp * 16 + (lane & 15)) * QS + (lane >> 4) * 8);
   for (int kt = 0; kt < ntiles; ++kt) {
     const int buf = kt & 1;
     if (kt + 1 < ntiles) { load_tile(kt + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    const int64_t slot_ahead = (tid < kKeys && kt + 2 < ntiles) ? lookup(kt + 2) : -1;   // in flight during this tile's math
     __syncthreads();
+    if (warp_has_rows) {
     const bf16* kb = Ks + buf * kKeys * QS;
     const bf16* vb = Vs + buf * kKeys * VS;
     float s[8][4];
@@ -224,6 +240,7 @@ __global__ void __launch_bounds__(128) capped_attn_mma_kernel(const AttnArgs a, 
     }
     // scale, temperature, cap, causal mask; online softmax per row
     float mx[2] = {-INFINITY, -INFINITY};
+    const bool need_mask = kt * kKeys + kKeys - 1 > min_pos;   // warp-uniform: some key of the tile is hidden from some row
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
@@ -231,7 +248,7 @@ __global__ void __launch_bounds__(128) capped_attn_mma_kernel(const AttnArgs a, 
         const int i = e >> 1, j = kt * kKeys + nt * 8 + 2 * tq4 + (e & 1);
         float v = s[nt][e] * qscale[i];
         if (a.softcap > 0.f) v = a.softcap * fast_tanh(v * inv_cap);
-        v = j <= pos[i] ? v : -INFINITY;
+        if (need_mask) v = j <= pos[i] ? v : -INFINITY;
         s[nt][e] = v;
         mx[i] = fmaxf(mx[i], v);
       }
@@ -270,6 +287,8 @@ __global__ void __launch_bounds__(128) capped_attn_mma_kernel(const AttnArgs a, 
         mma_bf16_16816(o[2 * vp + 1], pf, bv[2], bv[3]);
       }
     }
+    }
+    if (tid < kKeys) slot_s[kt & 1][tid] = slot_ahead;   // tile kt's slots were consumed by load_tile(kt) an iteration ago
     __syncthreads();   // everyone is done with this buffer before the next load overwrites it
   }
 #pragma unroll
@@ -298,7 +317,7 @@ int launch_mma(const AttnArgs& a, const int32_t* cu_tokens, int n_seqs, cudaStre
   const size_t smem = (static_cast<size_t>(kRows) * (DMAX + 8) + 2 * kKeys * (DMAX + 8) + 2 * kKeys * (VMAX + 8)) * sizeof(bf16);
   NVLLM_SMEM_ATTR_ONCE((capped_attn_mma_kernel<DMAX, VMAX>), smem);
   dim3 grid((a.n + tq - 1) / tq + n_seqs, a.kv_heads);
-  capped_attn_mma_kernel<DMAX, VMAX><<<grid, 128, smem, st>>>(a, cu_tokens, n_seqs, tq, group);
+  capped_attn_mma_kernel<DMAX, VMAX><<<grid, kThreads, smem, st>>>(a, cu_tokens, n_seqs, tq, group);
   NVLLM_LAUNCH_CHECK("capped_attn_mma_kernel");
   return 0;
 }

@@ -554,8 +554,12 @@ class Talapel : public ModelImpl {
         pend.a[0] = left_out_; pend.s[0] = 1.0f;
       }
       if (L.ffk == kDense) {
-        RUN(lin(gu_buf_, normed_, L.gu, 2 * L.ff, W, 2 * L.ff, dt_, "gate_up projection"));
-        RUN(nvllm_ff_activation(act_, gu_buf_, N, L.ff, 0, dt_, st)); ++launches; mk("ff_activation (silu gate)");
+        if (dt_ == NVLLM_BF16 && L.ff % 128 == 0 && W % 64 == 0) {  // SiLU gate in the GEMM's epilogue: [N, 2 ff] never reaches HBM
+          RUN(nvllm_gemm_silu_mul_bf16(act_, normed_, L.gu, N, L.ff, W, W, W, L.ff, nullptr, 0, st)); ++launches; mk("gate_up projection + SiLU gate");
+        } else {
+          RUN(lin(gu_buf_, normed_, L.gu, 2 * L.ff, W, 2 * L.ff, dt_, "gate_up projection"));
+          RUN(nvllm_ff_activation(act_, gu_buf_, N, L.ff, 0, dt_, st)); ++launches; mk("ff_activation (silu gate)");
+        }
         RUN(lin(ff_out_, act_, L.down, W, L.ff, W, NVLLM_F32, "down projection"));
         pend.a[2] = ff_out_; pend.s[2] = 1.0f; pend.dt[2] = NVLLM_F32;
       } else if (L.ffk == kExperts) {

@@ -14,6 +14,8 @@
 //   nvllm_gated_group_norm    RMS norm over equal parts of a row with a SiLU gate before or after it
 // Everything here is f32: inputs, state, arithmetic.  Only nvllm_gated_group_norm writes the operand type (its output
 // feeds a projection).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace nvllm {
@@ -33,18 +35,20 @@ struct RecArgs {
 
 constexpr int kRecTile = 16;  // tokens staged per round
 
+__device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+
 // CTA = (head, sequence, slice of dv).  Thread (p, ns): column p of the state, rows [ns * NPT, (ns + 1) * NPT) in registers.
-// Per round, kRecTile tokens' k, q (rows of dk), v, a, b are staged in shared memory; the products need no further
-// synchronisation.  NSL row slices of one column sit in neighbouring lanes and are summed with shuffles.
+// kRecTile tokens' k, q (rows of dk), v, a, b are staged in shared memory with cp.async, two rounds deep: the copies of the
+// next round fly while this round's tokens are stepped through, and the steps themselves need no synchronisation.  NSL row
+// slices of one column sit in neighbouring lanes and are summed with shuffles.  vec: rows are 16-byte multiples.
 template <int NPT, int NSL>
-__global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a, int pb) {
-  extern __shared__ float sm[];
-  const int DKP = NPT * NSL;                       // padded dk
-  float* ks = sm;                                  // [tile][DKP]
-  float* qs = ks + kRecTile * DKP;                 // [tile][DKP]
-  float* vs = qs + kRecTile * DKP;                 // [tile][pb]
-  float* as = vs + kRecTile * pb;                  // [tile]
-  float* bs = as + kRecTile;                       // [tile]
+__global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a, int pb, int vec) {
+  extern __shared__ __align__(16) float sm[];
+  constexpr int DKP = NPT * NSL;                   // padded dk
+  const int pbp = (pb + 3) & ~3;
+  const int stage = kRecTile * (2 * DKP + pbp + 2);
   const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * pb;
   const int tid = threadIdx.x, ns = tid % NSL, pl = tid / NSL, p = p0 + pl;
   const bool live = pl < pb && p < a.dv;
@@ -57,6 +61,50 @@ __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a,
     return;
   }
   const int g = h / a.group_div;
+  // both stages start as zeros (rows beyond dk and columns beyond dv stay zero) with a step of 1
+  for (int e = tid; e < 2 * stage; e += blockDim.x) sm[e] = 0.f;
+  __syncthreads();
+  if (a.step == nullptr && tid < 2 * kRecTile) sm[(tid / kRecTile) * stage + kRecTile * (2 * DKP + pbp) + kRecTile + tid % kRecTile] = 1.f;
+  const int ncol = min(pb, a.dv - p0);
+  auto issue = [&](int tb, int buf) {
+    float* ks = sm + buf * stage;
+    float* qs = ks + kRecTile * DKP;
+    float* vs = qs + kRecTile * DKP;
+    float* as = vs + kRecTile * pbp;
+    float* bs = as + kRecTile;
+    const int cnt = min(kRecTile, t1 - tb);
+    if (vec) {
+      const int kch = a.dk / 4, vch = ncol / 4;
+      for (int e = tid; e < cnt * kch; e += blockDim.x) {
+        const int tt = e / kch, c = e - tt * kch;
+        const int64_t t = tb + tt;
+        cp_async_16(smem_u32(ks + tt * DKP + c * 4), a.k + t * a.ldk + static_cast<int64_t>(g) * a.dk + c * 4, 16);
+        cp_async_16(smem_u32(qs + tt * DKP + c * 4), a.q + t * a.ldq + static_cast<int64_t>(g) * a.dk + c * 4, 16);
+      }
+      for (int e = tid; e < cnt * vch; e += blockDim.x) {
+        const int tt = e / vch, c = e - tt * vch;
+        cp_async_16(smem_u32(vs + tt * pbp + c * 4), a.v + static_cast<int64_t>(tb + tt) * a.ldv + static_cast<int64_t>(h) * a.dv + p0 + c * 4, 16);
+      }
+    } else {
+      for (int e = tid; e < cnt * a.dk; e += blockDim.x) {
+        const int tt = e / a.dk, n = e - tt * a.dk;
+        const int64_t t = tb + tt;
+        cp_async_4(smem_u32(ks + tt * DKP + n), a.k + t * a.ldk + static_cast<int64_t>(g) * a.dk + n);
+        cp_async_4(smem_u32(qs + tt * DKP + n), a.q + t * a.ldq + static_cast<int64_t>(g) * a.dk + n);
+      }
+      for (int e = tid; e < cnt * ncol; e += blockDim.x) {
+        const int tt = e / ncol, c = e - tt * ncol;
+        cp_async_4(smem_u32(vs + tt * pbp + c), a.v + static_cast<int64_t>(tb + tt) * a.ldv + static_cast<int64_t>(h) * a.dv + p0 + c);
+      }
+    }
+    if (tid < cnt) {
+      const int64_t t = tb + tid;
+      cp_async_4(smem_u32(as + tid), a.decay + (a.decay_ld ? t * a.decay_ld + h : h));
+      if (a.step) cp_async_4(smem_u32(bs + tid), a.step + (a.step_ld ? t * a.step_ld + h : h));
+    }
+    cp_async_commit();
+  };
+  issue(t0, 0);
   float S[NPT];
   float* sp = a.state + ((static_cast<int64_t>(slot) * a.heads + h) * a.dk) * a.dv;
   const bool fresh = a.positions[t0] == 0;
@@ -66,39 +114,35 @@ __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a,
     S[i] = (!fresh && live && n < a.dk) ? sp[static_cast<int64_t>(n) * a.dv + p] : 0.f;
   }
   const float d = a.skip ? a.skip[h] : 0.f;
-  for (int tb = t0; tb < t1; tb += kRecTile) {
+  int buf = 0;
+  for (int tb = t0; tb < t1; tb += kRecTile, buf ^= 1) {
     const int cnt = min(kRecTile, t1 - tb);
+    if (tb + kRecTile < t1) { issue(tb + kRecTile, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
     __syncthreads();
-    for (int e = tid; e < cnt * DKP; e += blockDim.x) {
-      const int tt = e / DKP, n = e % DKP;
-      const int64_t t = tb + tt;
-      ks[e] = n < a.dk ? a.k[t * a.ldk + static_cast<int64_t>(g) * a.dk + n] : 0.f;
-      qs[e] = n < a.dk ? a.q[t * a.ldq + static_cast<int64_t>(g) * a.dk + n] : 0.f;
-    }
-    for (int e = tid; e < cnt * pb; e += blockDim.x) {
-      const int tt = e / pb, c = e % pb;
-      vs[e] = p0 + c < a.dv ? a.v[(tb + tt) * a.ldv + static_cast<int64_t>(h) * a.dv + p0 + c] : 0.f;
-    }
-    if (tid < cnt) {
-      const int64_t t = tb + tid;
-      as[tid] = a.decay[a.decay_ld ? t * a.decay_ld + h : h];
-      bs[tid] = a.step ? a.step[a.step_ld ? t * a.step_ld + h : h] : 1.f;
-    }
-    __syncthreads();
+    const float* ks = sm + buf * stage;
+    const float* qs = ks + kRecTile * DKP;
+    const float* vs = qs + kRecTile * DKP;
+    const float* as = vs + kRecTile * pbp;
+    const float* bs = as + kRecTile;
     for (int tt = 0; tt < cnt; ++tt) {
-      const float av = as[tt], xv = vs[tt * pb + (pl < pb ? pl : 0)], bv = bs[tt] * xv;
-      const float* kr = ks + tt * DKP + ns * NPT;
-      const float* qr = qs + tt * DKP + ns * NPT;
-      float acc = 0.f;
+      const float av = as[tt], xv = vs[tt * pbp + (pl < pb ? pl : 0)], bv = bs[tt] * xv;
+      const float4* kr = reinterpret_cast<const float4*>(ks + tt * DKP + ns * NPT);   // broadcast reads, 16 bytes each
+      const float4* qr = reinterpret_cast<const float4*>(qs + tt * DKP + ns * NPT);
+      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        S[i] = fmaf(av, S[i], bv * kr[i]);
-        acc = fmaf(S[i], qr[i], acc);
+      for (int i = 0; i < NPT / 4; ++i) {
+        const float4 k4 = kr[i], q4 = qr[i];
+        S[4 * i] = fmaf(av, S[4 * i], bv * k4.x);         acc0 = fmaf(S[4 * i], q4.x, acc0);
+        S[4 * i + 1] = fmaf(av, S[4 * i + 1], bv * k4.y); acc1 = fmaf(S[4 * i + 1], q4.y, acc1);
+        S[4 * i + 2] = fmaf(av, S[4 * i + 2], bv * k4.z); acc2 = fmaf(S[4 * i + 2], q4.z, acc2);
+        S[4 * i + 3] = fmaf(av, S[4 * i + 3], bv * k4.w); acc3 = fmaf(S[4 * i + 3], q4.w, acc3);
       }
+      float acc = (acc0 + acc1) + (acc2 + acc3);
 #pragma unroll
       for (int o = 1; o < NSL; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (live && ns == 0) a.y[(tb + tt) * a.ldy + static_cast<int64_t>(h) * a.dv + p] = fmaf(d, xv, acc);
     }
+    __syncthreads();   // the round after next overwrites this stage
   }
   if (live) {
 #pragma unroll
@@ -121,16 +165,16 @@ struct ConvArgs {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 
 // out[t, c] = act(b[c] + sum_j w[c, j] * in(position(t) - (taps - 1 - j), c)); inputs before the portion come from the
-// state, inputs before the sequence are zero.
-__global__ void causal_conv_kernel(const ConvArgs a) {
-  const int64_t total = static_cast<int64_t>(a.n) * a.channels;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int t = static_cast<int>(i / a.channels), c = static_cast<int>(i % a.channels);
-    const int s = a.tok_seq[t], slot = a.seq_slot[s];
+// state, inputs before the sequence are zero.  CTA = one token x a run of channels: the token's metadata is read once,
+// channels are contiguous across the threads.
+__global__ void __launch_bounds__(256) causal_conv_kernel(const ConvArgs a) {
+  const int t = blockIdx.x;
+  const int s = a.tok_seq[t], slot = a.seq_slot[s];
+  const int c0 = a.cu_tokens[s];
+  const int64_t p = a.positions[t], pf = a.positions[c0];
+  const float* st = slot >= 0 ? a.state + static_cast<int64_t>(slot) * (a.taps - 1) * a.channels : nullptr;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < a.channels; c += gridDim.y * blockDim.x) {
     if (slot < 0) { a.out[t * a.ldo + c] = 0.f; continue; }
-    const int c0 = a.cu_tokens[s];
-    const int64_t p = a.positions[t], pf = a.positions[c0];
-    const float* st = a.state + static_cast<int64_t>(slot) * (a.taps - 1) * a.channels;
     float acc = a.b ? a.b[c] : 0.f;
     for (int j = 0; j < a.taps; ++j) {
       const int back = a.taps - 1 - j;
@@ -257,10 +301,13 @@ int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t st) {
   // more CTAs when few (sequence, head) pairs would leave SMs idle: split the columns (each column is independent)
   while (pb > 32 && static_cast<int64_t>(a.heads) * n_seqs * ((a.dv + pb - 1) / pb) < sm_count() && pb % 2 == 0) pb /= 2;
   const int threads = ((pb * NSL + 31) / 32) * 32;
-  const size_t smem = (static_cast<size_t>(kRecTile) * (2 * NPT * NSL + pb) + 2 * kRecTile) * sizeof(float);
+  const size_t smem = 2 * static_cast<size_t>(kRecTile) * (2 * NPT * NSL + ((pb + 3) & ~3) + 2) * sizeof(float);
   dim3 grid(a.heads, n_seqs, (a.dv + pb - 1) / pb);
   if (smem > 48 * 1024) NVLLM_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<NPT, NSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  linear_recurrence_kernel<NPT, NSL><<<grid, threads, smem, st>>>(a, pb);
+  // 16-byte copies when every staged row starts and ends on a 16-byte boundary
+  const int vec = a.dk % 4 == 0 && a.dv % 4 == 0 && pb % 4 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && a.ldv % 4 == 0 && aligned16(a.q) &&
+                  aligned16(a.k) && aligned16(a.v);
+  linear_recurrence_kernel<NPT, NSL><<<grid, threads, smem, st>>>(a, pb, vec);
   NVLLM_LAUNCH_CHECK("linear_recurrence_kernel");
   return 0;
 }
@@ -298,7 +345,8 @@ extern "C" int nvllm_causal_conv(float* out, int64_t ldo, const float* in, int64
   NVLLM_CHECK_ARG(out && in && w && state && tok_seq && seq_slot && cu_tokens && positions && out != in, NVLLM_ERR_ARG, "causal_conv: NULL");
   ConvArgs a{out, ldo, in, ldi, w, bias, state, tok_seq, seq_slot, cu_tokens, positions, n, channels, taps, silu};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  causal_conv_kernel<<<grid_for(static_cast<int64_t>(n) * channels), 256, 0, st>>>(a);
+  dim3 grid(static_cast<unsigned>(n), static_cast<unsigned>(std::min(8, (channels + 255) / 256)));
+  causal_conv_kernel<<<grid, 256, 0, st>>>(a);
   NVLLM_LAUNCH_CHECK("causal_conv_kernel");
   if (taps > 1) {
     conv_state_kernel<<<grid_for(static_cast<int64_t>(n_seqs) * channels), 256, 0, st>>>(a, n_seqs);
