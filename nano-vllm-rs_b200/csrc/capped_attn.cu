@@ -132,9 +132,85 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
 // cap, mask and the online softmax in f32.  Key tiles start at multiples of 64 from the sequence's first key whatever the
 // portion, so a row's result does not depend on how the prompt was cut.  Head sizes are padded to DMAX / VMAX with zeros in
 // shared memory.
+constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kWarps = 8, kRows = 16 * kWarps, kKeys = 64, kThreads = 32 * kWarps;
 
-__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
+// One MUFU instruction, relative error 2^-11: an absolute error of |s| * 5e-4 on a capped score s, far inside what bf16 keys
+// and queries carry (4e-3 relative) -- used by the bf16 tensor-core kernel only.
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// One warp's share of a key tile: 16 rows x (16 NP) keys -> S on tensor cores, cap / mask / online softmax in f32, then
+// O[:, 0 .. 16 VP) += P . V.  k_addr / v_addr are the warp's ldmatrix lane addresses of its first key (and first value column).
+template <int DMAX, int VMAX, int NP, int VP, int QS, int VS>
+__device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2], float (&l)[2], uint32_t q_addr, uint32_t k_addr,
+                                          uint32_t v_addr, int key0, const int (&pos)[2], const float (&qscale)[2], bool capped, float cap2,
+                                          bool need_mask, int tq4) {
+  float s[2 * NP][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NP; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < DMAX / 16; ++kk) {
+    uint32_t af[4];
+    ldmatrix_x4(af, q_addr + kk * 32);
+#pragma unroll
+    for (int np = 0; np < NP; ++np) {
+      uint32_t bk[4];
+      ldmatrix_x4(bk, k_addr + np * 16 * QS * 2 + kk * 32);
+      mma_bf16_16816(s[2 * np], af, bk[0], bk[1]);
+      mma_bf16_16816(s[2 * np + 1], af, bk[2], bk[3]);
+    }
+  }
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 2 * NP; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int i = e >> 1, j = key0 + nt * 8 + 2 * tq4 + (e & 1);
+      float v = s[nt][e] * qscale[i];            // with a cap: the score over the cap; without: the score in log2 units
+      if (capped) v = cap2 * fast_tanh(v);
+      if (need_mask) v = j <= pos[i] ? v : -INFINITY;
+      s[nt][e] = v;
+      mx[i] = fmaxf(mx[i], v);
+    }
+  float corr[2], mu[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+    const float mn = fmaxf(m[i], mx[i]);
+    mu[i] = mn == -INFINITY ? 0.f : mn;
+    corr[i] = fast_exp2(m[i] - mu[i]);
+    m[i] = mn;
+    l[i] *= corr[i];
+  }
+#pragma unroll
+  for (int nt = 0; nt < 2 * NP; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float p = fast_exp2(s[nt][e] - mu[e >> 1]);
+      s[nt][e] = p;
+      l[e >> 1] += p;
+    }
+#pragma unroll
+  for (int i = 0; i < 2 * VP; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+#pragma unroll
+  for (int kc2 = 0; kc2 < NP; ++kc2) {
+    uint32_t pf[4];
+    pf[0] = pack_bf16x2(s[2 * kc2][0], s[2 * kc2][1]); pf[1] = pack_bf16x2(s[2 * kc2][2], s[2 * kc2][3]);
+    pf[2] = pack_bf16x2(s[2 * kc2 + 1][0], s[2 * kc2 + 1][1]); pf[3] = pack_bf16x2(s[2 * kc2 + 1][2], s[2 * kc2 + 1][3]);
+#pragma unroll
+    for (int vp = 0; vp < VP; ++vp) {
+      uint32_t bv[4];
+      ldmatrix_x4_trans(bv, v_addr + kc2 * 16 * VS * 2 + vp * 32);
+      mma_bf16_16816(o[2 * vp], pf, bv[0], bv[1]);
+      mma_bf16_16816(o[2 * vp + 1], pf, bv[2], bv[3]);
+    }
+  }
+}
 
 template <int DMAX, int VMAX>
 __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const AttnArgs a, const int32_t* __restrict__ cu_tokens, int n_seqs, int tq,
@@ -191,102 +267,52 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
     for (int c = lh; c < vch; c += 4) cp_async_16(smem_u32(vd + c * 8), vsrc + (nb ? c * 8 : 0), nb);
     cp_async_commit();
   };
-  // this thread's two rows
+  // Few rows (single tokens: at most 16 (token, head) pairs): all warps work on the SAME 16 rows, warp w on the keys
+  // [16 (w & 3), +16) of every tile and half (w >> 2) of the value columns; the four partial softmaxes are merged at the end.
+  // Otherwise warp w owns rows [16 w, +16) and walks whole tiles (warps without rows only help with the copies).
+  const bool few = ntok * group <= 16;
+  const int rbase = few ? 0 : warp * 16, kq = warp & 3, vh = warp >> 2;
   int pos[2]; float qscale[2]; bool valid[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int r = warp * 16 + gq + 8 * i, t = r / group;
+    const int r = rbase + gq + 8 * i, t = r / group;
     valid[i] = t < ntok && r < tq * group;
     pos[i] = valid[i] ? static_cast<int>(a.positions[tok0 + t]) : -1;
-    qscale[i] = a.scale * (1.0f + a.temp_coef * logf(floorf(static_cast<float>((pos[i] + 1) / a.temp_every)) + 1.0f));
+    qscale[i] = a.scale * (1.0f + a.temp_coef * logf(floorf(static_cast<float>((pos[i] + 1) / a.temp_every)) + 1.0f)) *
+                (a.softcap > 0.f ? 1.0f / a.softcap : kLog2e);
   }
-  // rows of a warp: 16 consecutive (token, head) pairs; the first decides whether the warp has any, the smallest position
-  // whether a tile needs the causal mask (empty rows count as hidden)
-  const bool warp_has_rows = (warp * 16) / group < ntok;
+  // the smallest position of the warp's rows decides whether a tile needs the causal mask (empty rows count as hidden)
+  const bool warp_has_rows = rbase / group < ntok;
   const int min_pos = __reduce_min_sync(0xffffffffu, min(pos[0], pos[1]));
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float o[VMAX / 8][4];
 #pragma unroll
   for (int i = 0; i < VMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-  const float inv_cap = a.softcap > 0.f ? 1.0f / a.softcap : 0.f;
+  const bool capped = a.softcap > 0.f;
+  const float cap2 = a.softcap * kLog2e;           // scores are kept in log2 units: softmax with exp2
   const int ntiles = (nkeys + kKeys - 1) / kKeys;
   if (tid < kKeys) { slot_s[0][tid] = lookup(0); slot_s[1][tid] = lookup(1); }
   __syncthreads();
   load_tile(0, 0);
-  const uint32_t q_addr = smem_u32(Qs + (warp * 16 + (lane & 15)) * QS + (lane >> 4) * 8);
+  const uint32_t q_addr = smem_u32(Qs + (rbase + (lane & 15)) * QS + (lane >> 4) * 8);
+  const int k_lane = ((lane & 7) + (lane >> 4) * 8) * QS + ((lane >> 3) & 1) * 8;
+  const int v_lane = ((lane & 7) + ((lane >> 3) & 1) * 8) * VS + (lane >> 4) * 8;
   for (int kt = 0; kt < ntiles; ++kt) {
     const int buf = kt & 1;
     if (kt + 1 < ntiles) { load_tile(kt + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
     const int64_t slot_ahead = (tid < kKeys && kt + 2 < ntiles) ? lookup(kt + 2) : -1;   // in flight during this tile's math
     __syncthreads();
-    if (warp_has_rows) {
     const bf16* kb = Ks + buf * kKeys * QS;
     const bf16* vb = Vs + buf * kKeys * VS;
-    float s[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-    const uint32_t k_addr = smem_u32(kb + ((lane & 7) + (lane >> 4) * 8) * QS + ((lane >> 3) & 1) * 8);
-#pragma unroll
-    for (int kk = 0; kk < DMAX / 16; ++kk) {
-      uint32_t af[4];
-      ldmatrix_x4(af, q_addr + kk * 32);
-#pragma unroll
-      for (int np = 0; np < 4; ++np) {
-        uint32_t bk[4];
-        ldmatrix_x4(bk, k_addr + np * 16 * QS * 2 + kk * 32);
-        mma_bf16_16816(s[2 * np], af, bk[0], bk[1]);
-        mma_bf16_16816(s[2 * np + 1], af, bk[2], bk[3]);
-      }
-    }
-    // scale, temperature, cap, causal mask; online softmax per row
-    float mx[2] = {-INFINITY, -INFINITY};
-    const bool need_mask = kt * kKeys + kKeys - 1 > min_pos;   // warp-uniform: some key of the tile is hidden from some row
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1, j = kt * kKeys + nt * 8 + 2 * tq4 + (e & 1);
-        float v = s[nt][e] * qscale[i];
-        if (a.softcap > 0.f) v = a.softcap * fast_tanh(v * inv_cap);
-        if (need_mask) v = j <= pos[i] ? v : -INFINITY;
-        s[nt][e] = v;
-        mx[i] = fmaxf(mx[i], v);
-      }
-    float corr[2], mu[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
-      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-      const float mn = fmaxf(m[i], mx[i]);
-      mu[i] = mn == -INFINITY ? 0.f : mn;
-      corr[i] = __expf(m[i] - mu[i]);
-      m[i] = mn;
-      l[i] *= corr[i];
-    }
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = __expf(s[nt][e] - mu[e >> 1]);
-        s[nt][e] = p;
-        l[e >> 1] += p;
-      }
-#pragma unroll
-    for (int i = 0; i < VMAX / 8; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
-    const uint32_t v_addr = smem_u32(vb + ((lane & 7) + ((lane >> 3) & 1) * 8) * VS + (lane >> 4) * 8);
-#pragma unroll
-    for (int kc2 = 0; kc2 < 4; ++kc2) {
-      uint32_t pf[4];
-      pf[0] = pack_bf16x2(s[2 * kc2][0], s[2 * kc2][1]); pf[1] = pack_bf16x2(s[2 * kc2][2], s[2 * kc2][3]);
-      pf[2] = pack_bf16x2(s[2 * kc2 + 1][0], s[2 * kc2 + 1][1]); pf[3] = pack_bf16x2(s[2 * kc2 + 1][2], s[2 * kc2 + 1][3]);
-#pragma unroll
-      for (int vp = 0; vp < VMAX / 16; ++vp) {
-        uint32_t bv[4];
-        ldmatrix_x4_trans(bv, v_addr + kc2 * 16 * VS * 2 + vp * 32);
-        mma_bf16_16816(o[2 * vp], pf, bv[0], bv[1]);
-        mma_bf16_16816(o[2 * vp + 1], pf, bv[2], bv[3]);
-      }
-    }
+    if (few) {
+      const int key0 = kt * kKeys + kq * 16;
+      if (key0 < nkeys)
+        attn_tile<DMAX, VMAX, 1, VMAX / 32, QS, VS>(o, m, l, q_addr, smem_u32(kb + kq * 16 * QS + k_lane),
+                                                    smem_u32(vb + kq * 16 * VS + vh * (VMAX / 2) + v_lane), key0, pos, qscale, capped, cap2,
+                                                    key0 + 15 > min_pos, tq4);
+    } else if (warp_has_rows) {
+      attn_tile<DMAX, VMAX, 4, VMAX / 16, QS, VS>(o, m, l, q_addr, smem_u32(kb + k_lane), smem_u32(vb + v_lane), kt * kKeys, pos, qscale, capped,
+                                                  cap2, kt * kKeys + kKeys - 1 > min_pos, tq4);
     }
     if (tid < kKeys) slot_s[kt & 1][tid] = slot_ahead;   // tile kt's slots were consumed by load_tile(kt) an iteration ago
     __syncthreads();   // everyone is done with this buffer before the next load overwrites it
@@ -295,6 +321,43 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   for (int i = 0; i < 2; ++i) {
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  if (few) {
+    // merge the four key quarters: (m, l) per quarter and row, O per quarter, row and column, through the (now idle) tile memory
+    float* ms = reinterpret_cast<float*>(Ks);          // [4][16]
+    float* ls = ms + 64;                               // [4][16]
+    float* os = ls + 64;                               // [4][16][VMAX]
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = gq + 8 * i;
+      if (vh == 0 && tq4 == 0) { ms[kq * 16 + r] = m[i]; ls[kq * 16 + r] = l[i]; }
+#pragma unroll
+      for (int vt = 0; vt < VMAX / 16; ++vt) {
+        const int c = vh * (VMAX / 2) + vt * 8 + 2 * tq4;
+        os[(kq * 16 + r) * VMAX + c] = o[vt][2 * i];
+        os[(kq * 16 + r) * VMAX + c + 1] = o[vt][2 * i + 1];
+      }
+    }
+    __syncthreads();
+    const int rows = ntok * group;
+    for (int e = tid; e < rows * a.vdim; e += kThreads) {
+      const int r = e / a.vdim, c = e - r * a.vdim, t = r / group, h = g * group + r % group;
+      const float mm = fmaxf(fmaxf(ms[r], ms[16 + r]), fmaxf(ms[32 + r], ms[48 + r]));
+      float num = 0.f, den = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float w = fast_exp2(ms[k * 16 + r] - mm);     // a quarter that saw no key: exp2(-inf) = 0
+        num = fmaf(w, os[(k * 16 + r) * VMAX + c], num);
+        den = fmaf(w, ls[k * 16 + r], den);
+      }
+      float v = den > 0.f ? num / den : 0.f;
+      if (a.gate) v *= 1.0f / (1.0f + __expf(-a.gate[static_cast<int64_t>(tok0 + t) * a.ldg + static_cast<int64_t>(h) * a.vdim + c]));
+      static_cast<bf16*>(a.out)[static_cast<int64_t>(tok0 + t) * a.ldo + static_cast<int64_t>(h) * a.vdim + c] = __float2bfloat16_rn(v);
+    }
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
     if (!valid[i]) continue;
     const int r = warp * 16 + gq + 8 * i, t = r / group, h = g * group + r % group;
     const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;

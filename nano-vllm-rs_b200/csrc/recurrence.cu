@@ -39,25 +39,33 @@ __device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void* gptr)
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
 }
 
-// CTA = (head, sequence, slice of dv).  Thread (p, ns): column p of the state, rows [ns * NPT, (ns + 1) * NPT) in registers.
+// CTA = (head, sequence, slice of dv).  Thread (pc, ns): PP neighbouring columns of the state, rows [ns * NPT, (ns + 1) * NPT) of
+// each in registers (every k / q value read from shared memory serves PP columns: the broadcast reads are what binds).
 // kRecTile tokens' k, q (rows of dk), v, a, b are staged in shared memory with cp.async, two rounds deep: the copies of the
 // next round fly while this round's tokens are stepped through, and the steps themselves need no synchronisation.  NSL row
 // slices of one column sit in neighbouring lanes and are summed with shuffles.  vec: rows are 16-byte multiples.
-template <int NPT, int NSL>
+template <int NPT, int NSL, int PP>
 __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a, int pb, int vec) {
   extern __shared__ __align__(16) float sm[];
-  constexpr int DKP = NPT * NSL;                   // padded dk
+  // a row of k (or q) in shared memory: NSL slices of NPT values, each followed by 4 floats of padding, so that the NSL
+  // 16-byte broadcast reads of one warp instruction (one per slice) fall into different banks
+  constexpr int SL = NPT + 4, DKP = SL * NSL;
   const int pbp = (pb + 3) & ~3;
   const int stage = kRecTile * (2 * DKP + pbp + 2);
   const int h = blockIdx.x, s = blockIdx.y, p0 = blockIdx.z * pb;
-  const int tid = threadIdx.x, ns = tid % NSL, pl = tid / NSL, p = p0 + pl;
-  const bool live = pl < pb && p < a.dv;
+  // the thread's PP columns lie pb / PP apart, so that neighbouring threads hold neighbouring columns (coalesced state)
+  const int tid = threadIdx.x, ns = tid % NSL, pl = tid / NSL, p = p0 + pl, half = (pb + PP - 1) / PP;
+  bool live[PP];
+#pragma unroll
+  for (int j = 0; j < PP; ++j) live[j] = pl < half && pl + j * half < pb && p + j * half < a.dv;
   const int t0 = a.cu_tokens[s], t1 = a.cu_tokens[s + 1];
   const int slot = a.seq_slot[s];
   if (t1 <= t0) return;
   if (slot < 0) {  // padding sequence of a captured batch: defined output, no state
     for (int t = t0; t < t1; ++t)
-      if (live && ns == 0) a.y[t * a.ldy + static_cast<int64_t>(h) * a.dv + p] = 0.f;
+#pragma unroll
+      for (int j = 0; j < PP; ++j)
+        if (live[j] && ns == 0) a.y[t * a.ldy + static_cast<int64_t>(h) * a.dv + p + j * half] = 0.f;
     return;
   }
   const int g = h / a.group_div;
@@ -78,8 +86,9 @@ __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a,
       for (int e = tid; e < cnt * kch; e += blockDim.x) {
         const int tt = e / kch, c = e - tt * kch;
         const int64_t t = tb + tt;
-        cp_async_16(smem_u32(ks + tt * DKP + c * 4), a.k + t * a.ldk + static_cast<int64_t>(g) * a.dk + c * 4, 16);
-        cp_async_16(smem_u32(qs + tt * DKP + c * 4), a.q + t * a.ldq + static_cast<int64_t>(g) * a.dk + c * 4, 16);
+        const int dst = tt * DKP + (c * 4 / NPT) * SL + (c * 4) % NPT;
+        cp_async_16(smem_u32(ks + dst), a.k + t * a.ldk + static_cast<int64_t>(g) * a.dk + c * 4, 16);
+        cp_async_16(smem_u32(qs + dst), a.q + t * a.ldq + static_cast<int64_t>(g) * a.dk + c * 4, 16);
       }
       for (int e = tid; e < cnt * vch; e += blockDim.x) {
         const int tt = e / vch, c = e - tt * vch;
@@ -89,8 +98,9 @@ __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a,
       for (int e = tid; e < cnt * a.dk; e += blockDim.x) {
         const int tt = e / a.dk, n = e - tt * a.dk;
         const int64_t t = tb + tt;
-        cp_async_4(smem_u32(ks + tt * DKP + n), a.k + t * a.ldk + static_cast<int64_t>(g) * a.dk + n);
-        cp_async_4(smem_u32(qs + tt * DKP + n), a.q + t * a.ldq + static_cast<int64_t>(g) * a.dk + n);
+        const int dst = tt * DKP + (n / NPT) * SL + n % NPT;
+        cp_async_4(smem_u32(ks + dst), a.k + t * a.ldk + static_cast<int64_t>(g) * a.dk + n);
+        cp_async_4(smem_u32(qs + dst), a.q + t * a.ldq + static_cast<int64_t>(g) * a.dk + n);
       }
       for (int e = tid; e < cnt * ncol; e += blockDim.x) {
         const int tt = e / ncol, c = e - tt * ncol;
@@ -105,14 +115,16 @@ __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a,
     cp_async_commit();
   };
   issue(t0, 0);
-  float S[NPT];
+  float S[PP][NPT];
   float* sp = a.state + ((static_cast<int64_t>(slot) * a.heads + h) * a.dk) * a.dv;
   const bool fresh = a.positions[t0] == 0;
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) {
-    const int n = ns * NPT + i;
-    S[i] = (!fresh && live && n < a.dk) ? sp[static_cast<int64_t>(n) * a.dv + p] : 0.f;
-  }
+  for (int j = 0; j < PP; ++j)
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int n = ns * NPT + i;
+      S[j][i] = (!fresh && live[j] && n < a.dk) ? sp[static_cast<int64_t>(n) * a.dv + p + j * half] : 0.f;
+    }
   const float d = a.skip ? a.skip[h] : 0.f;
   int buf = 0;
   for (int tb = t0; tb < t1; tb += kRecTile, buf ^= 1) {
@@ -125,32 +137,39 @@ __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a,
     const float* as = vs + kRecTile * pbp;
     const float* bs = as + kRecTile;
     for (int tt = 0; tt < cnt; ++tt) {
-      const float av = as[tt], xv = vs[tt * pbp + (pl < pb ? pl : 0)], bv = bs[tt] * xv;
-      const float4* kr = reinterpret_cast<const float4*>(ks + tt * DKP + ns * NPT);   // broadcast reads, 16 bytes each
-      const float4* qr = reinterpret_cast<const float4*>(qs + tt * DKP + ns * NPT);
-      float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+      const float av = as[tt], bt = bs[tt];
+      float xv[PP], bv[PP], acc[PP];
+#pragma unroll
+      for (int j = 0; j < PP; ++j) { xv[j] = vs[tt * pbp + (live[j] ? pl + j * half : 0)]; bv[j] = bt * xv[j]; acc[j] = 0.f; }
+      const float4* kr = reinterpret_cast<const float4*>(ks + tt * DKP + ns * SL);   // broadcast reads, 16 bytes each
+      const float4* qr = reinterpret_cast<const float4*>(qs + tt * DKP + ns * SL);
 #pragma unroll
       for (int i = 0; i < NPT / 4; ++i) {
         const float4 k4 = kr[i], q4 = qr[i];
-        S[4 * i] = fmaf(av, S[4 * i], bv * k4.x);         acc0 = fmaf(S[4 * i], q4.x, acc0);
-        S[4 * i + 1] = fmaf(av, S[4 * i + 1], bv * k4.y); acc1 = fmaf(S[4 * i + 1], q4.y, acc1);
-        S[4 * i + 2] = fmaf(av, S[4 * i + 2], bv * k4.z); acc2 = fmaf(S[4 * i + 2], q4.z, acc2);
-        S[4 * i + 3] = fmaf(av, S[4 * i + 3], bv * k4.w); acc3 = fmaf(S[4 * i + 3], q4.w, acc3);
-      }
-      float acc = (acc0 + acc1) + (acc2 + acc3);
 #pragma unroll
-      for (int o = 1; o < NSL; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && ns == 0) a.y[(tb + tt) * a.ldy + static_cast<int64_t>(h) * a.dv + p] = fmaf(d, xv, acc);
+        for (int j = 0; j < PP; ++j) {
+          S[j][4 * i] = fmaf(av, S[j][4 * i], bv[j] * k4.x);         acc[j] = fmaf(S[j][4 * i], q4.x, acc[j]);
+          S[j][4 * i + 1] = fmaf(av, S[j][4 * i + 1], bv[j] * k4.y); acc[j] = fmaf(S[j][4 * i + 1], q4.y, acc[j]);
+          S[j][4 * i + 2] = fmaf(av, S[j][4 * i + 2], bv[j] * k4.z); acc[j] = fmaf(S[j][4 * i + 2], q4.z, acc[j]);
+          S[j][4 * i + 3] = fmaf(av, S[j][4 * i + 3], bv[j] * k4.w); acc[j] = fmaf(S[j][4 * i + 3], q4.w, acc[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < PP; ++j) {
+#pragma unroll
+        for (int o = 1; o < NSL; o <<= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+        if (live[j] && ns == 0) a.y[(tb + tt) * a.ldy + static_cast<int64_t>(h) * a.dv + p + j * half] = fmaf(d, xv[j], acc[j]);
+      }
     }
     __syncthreads();   // the round after next overwrites this stage
   }
-  if (live) {
+#pragma unroll
+  for (int j = 0; j < PP; ++j)
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
       const int n = ns * NPT + i;
-      if (n < a.dk) sp[static_cast<int64_t>(n) * a.dv + p] = S[i];
+      if (live[j] && n < a.dk) sp[static_cast<int64_t>(n) * a.dv + p + j * half] = S[j][i];
     }
-  }
 }
 
 struct ConvArgs {
@@ -186,6 +205,48 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const ConvArgs a) {
       acc = fmaf(a.w[static_cast<int64_t>(c) * a.taps + j], x, acc);
     }
     a.out[t * a.ldo + c] = a.silu ? silu_f(acc) : acc;
+  }
+}
+
+// The same for short windows (TAPS <= 4), one thread per channel walking a run of tokens with the window in registers: every
+// input is read once.  Where a run enters a new sequence the window is rebuilt from the batch or the sequence's state.
+template <int TAPS>
+__global__ void __launch_bounds__(256) causal_conv_window_kernel(const ConvArgs a, int run) {
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  float w[TAPS], win[TAPS > 1 ? TAPS - 1 : 1];
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) w[j] = a.w[static_cast<int64_t>(c) * TAPS + j];
+  const float bias = a.b ? a.b[c] : 0.f;
+  const int t_begin = blockIdx.x * run, t_end = min(a.n, t_begin + run);
+  int cur = -1, slot = -1;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int s = a.tok_seq[t];
+    if (s != cur) {
+      cur = s;
+      slot = a.seq_slot[s];
+      const int c0 = a.cu_tokens[s];
+      const int64_t p = a.positions[t], pf = a.positions[c0];
+#pragma unroll
+      for (int k = 0; k < TAPS - 1; ++k) {
+        const int back = TAPS - 1 - k;
+        const int64_t ps = p - back;
+        float x = 0.f;
+        if (slot >= 0 && ps >= 0)
+          x = t - back >= c0 ? a.in[static_cast<int64_t>(t - back) * a.ldi + c]
+                             : a.state[(static_cast<int64_t>(slot) * (TAPS - 1) + (ps - (pf - (TAPS - 1)))) * a.channels + c];
+        win[k] = x;
+      }
+    }
+    if (slot < 0) { a.out[t * a.ldo + c] = 0.f; continue; }
+    const float x = a.in[static_cast<int64_t>(t) * a.ldi + c];
+    float acc = fmaf(w[TAPS - 1], x, bias);
+#pragma unroll
+    for (int k = 0; k < TAPS - 1; ++k) acc = fmaf(w[k], win[k], acc);
+    a.out[t * a.ldo + c] = a.silu ? silu_f(acc) : acc;
+#pragma unroll
+    for (int k = 0; k + 1 < TAPS - 1; ++k) win[k] = win[k + 1];
+    if (TAPS > 1) win[TAPS - 2] = x;
   }
 }
 
@@ -293,21 +354,21 @@ inline unsigned grid_for(int64_t total) {
   return static_cast<unsigned>(b > cap ? cap : (b < 1 ? 1 : b));
 }
 
-template <int NPT, int NSL>
+template <int NPT, int NSL, int PP>
 int launch_recurrence(const RecArgs& a, int n_seqs, cudaStream_t st) {
   int pb = a.dv;                                  // columns per CTA
-  const int max_pb = 512 / NSL;
+  const int max_pb = 512 / NSL * PP;
   if (pb > max_pb) pb = max_pb;
   // more CTAs when few (sequence, head) pairs would leave SMs idle: split the columns (each column is independent)
   while (pb > 32 && static_cast<int64_t>(a.heads) * n_seqs * ((a.dv + pb - 1) / pb) < sm_count() && pb % 2 == 0) pb /= 2;
-  const int threads = ((pb * NSL + 31) / 32) * 32;
-  const size_t smem = 2 * static_cast<size_t>(kRecTile) * (2 * NPT * NSL + ((pb + 3) & ~3) + 2) * sizeof(float);
+  const int threads = (((pb + PP - 1) / PP * NSL + 31) / 32) * 32;
+  const size_t smem = 2 * static_cast<size_t>(kRecTile) * (2 * (NPT + 4) * NSL + ((pb + 3) & ~3) + 2) * sizeof(float);
   dim3 grid(a.heads, n_seqs, (a.dv + pb - 1) / pb);
-  if (smem > 48 * 1024) NVLLM_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<NPT, NSL>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  if (smem > 48 * 1024) NVLLM_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<NPT, NSL, PP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   // 16-byte copies when every staged row starts and ends on a 16-byte boundary
   const int vec = a.dk % 4 == 0 && a.dv % 4 == 0 && pb % 4 == 0 && a.ldq % 4 == 0 && a.ldk % 4 == 0 && a.ldv % 4 == 0 && aligned16(a.q) &&
                   aligned16(a.k) && aligned16(a.v);
-  linear_recurrence_kernel<NPT, NSL><<<grid, threads, smem, st>>>(a, pb, vec);
+  linear_recurrence_kernel<NPT, NSL, PP><<<grid, threads, smem, st>>>(a, pb, vec);
   NVLLM_LAUNCH_CHECK("linear_recurrence_kernel");
   return 0;
 }
@@ -329,11 +390,11 @@ extern "C" int nvllm_linear_recurrence(float* y, int64_t ldy, const float* q, in
   RecArgs a{y, ldy, q, k, v, ldq, ldk, ldv, heads / groups, decay, decay_per_token ? heads : 0, step, step_per_token ? heads : 0,
             skip, state, seq_slot, cu_tokens, positions, heads, dk, dv};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dk <= 16) return launch_recurrence<16, 1>(a, n_seqs, st);
-  if (dk <= 32) return launch_recurrence<32, 1>(a, n_seqs, st);
-  if (dk <= 64) return launch_recurrence<64, 1>(a, n_seqs, st);
-  if (dk <= 128) return launch_recurrence<64, 2>(a, n_seqs, st);
-  return launch_recurrence<64, 4>(a, n_seqs, st);
+  if (dk <= 16) return launch_recurrence<16, 1, 2>(a, n_seqs, st);
+  if (dk <= 32) return launch_recurrence<32, 1, 2>(a, n_seqs, st);
+  if (dk <= 64) return launch_recurrence<32, 2, 2>(a, n_seqs, st);
+  if (dk <= 128) return launch_recurrence<32, 4, 2>(a, n_seqs, st);
+  return launch_recurrence<32, 8, 2>(a, n_seqs, st);
 }
 
 extern "C" int nvllm_causal_conv(float* out, int64_t ldo, const float* in, int64_t ldi, const float* w, const float* bias, float* state,
@@ -345,8 +406,16 @@ extern "C" int nvllm_causal_conv(float* out, int64_t ldo, const float* in, int64
   NVLLM_CHECK_ARG(out && in && w && state && tok_seq && seq_slot && cu_tokens && positions && out != in, NVLLM_ERR_ARG, "causal_conv: NULL");
   ConvArgs a{out, ldo, in, ldi, w, bias, state, tok_seq, seq_slot, cu_tokens, positions, n, channels, taps, silu};
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  dim3 grid(static_cast<unsigned>(n), static_cast<unsigned>(std::min(8, (channels + 255) / 256)));
-  causal_conv_kernel<<<grid, 256, 0, st>>>(a);
+  if (taps >= 2 && taps <= 4 && n >= 8 * n_seqs) {   // runs of a sequence's tokens: worth a register window
+    const int run = 32;
+    dim3 grid(static_cast<unsigned>((n + run - 1) / run), static_cast<unsigned>((channels + 255) / 256));
+    if (taps == 2) causal_conv_window_kernel<2><<<grid, 256, 0, st>>>(a, run);
+    else if (taps == 3) causal_conv_window_kernel<3><<<grid, 256, 0, st>>>(a, run);
+    else causal_conv_window_kernel<4><<<grid, 256, 0, st>>>(a, run);
+  } else {
+    dim3 grid(static_cast<unsigned>(n), static_cast<unsigned>(std::min(8, (channels + 255) / 256)));
+    causal_conv_kernel<<<grid, 256, 0, st>>>(a);
+  }
   NVLLM_LAUNCH_CHECK("causal_conv_kernel");
   if (taps > 1) {
     conv_state_kernel<<<grid_for(static_cast<int64_t>(n_seqs) * channels), 256, 0, st>>>(a, n_seqs);
