@@ -772,12 +772,16 @@ def kernel_rooflines(z, arch, n_tok, ctx, decode, hbm, tf):
         out["causal_conv"] = (2 * n_tok * (inner + 2 * gn) * z["taps"], n_tok * (inner + 2 * gn) * 8)
         out["retention q k v g projection"] = gemm(2 * rq + 2 * rv, W)
         out["retention output projection"] = gemm(W, rv)
-        out["gate_up projection"] = gemm(2 * z["dense_ff"], W)
+        out["gate_up projection"] = out["gate_up projection + SiLU gate"] = gemm(2 * z["dense_ff"], W)
         out["down projection"] = gemm(W, z["dense_ff"])
         used = min(z["experts"], n_tok * z["top"])
         out["expert up grouped GEMM"] = (2 * n_tok * z["top"] * W * z["ff"], 2 * used * z["ff"] * W)
         out["expert down grouped GEMM"] = (2 * n_tok * z["top"] * W * z["ff"], 2 * used * z["ff"] * W)
-        return {k: max(f / (tf * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}
+        # The recurrences run in f32 by definition of the design (state and everything that enters it), so their compute
+        # bound is the f32 FMA rate of the CUDA cores, not the bf16 tensor peak: SMs x 128 lanes x 2 flop x max SM clock
+        # (nominal; the pool has no measured f32 figure).
+        f32_tf = 148 * 128 * 2 * 1.965e9 / 1e12
+        return {k: max(f / ((f32_tf if k.startswith("linear_recurrence") else tf) * 1e12), b / (hbm * 1e9)) * 1e6 for k, (f, b) in out.items()}
     if arch == "kosazen":
         r, rd, d, vd, E, ff, top, sff = z["kv_rank"], z["rot_dim"], z["dim"], z["vdim"], z["experts"], z["ff"], z["top"], z["shared_ff"]
         out["latent_attention"] = (2 * pairs * H * (2 * r + rd), (n_tok // max(1, L) if not decode else n_tok) * L * (r + rd) * 2 + n_tok * H * (2 * r + rd) * 4)

@@ -223,7 +223,11 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq4 = lane & 3;
   const int g = blockIdx.y;
   // which (sequence, token tile) is this CTA's
-  int tile = blockIdx.x, seq = -1, tok0 = 0, ntok = 0;
+  // (tiles late in a sequence see the most keys: they are handed out first, so that the last wave is made of short ones)
+  int total = 0;
+  for (int s = 0; s < n_seqs; ++s) total += (cu_tokens[s + 1] - cu_tokens[s] + tq - 1) / tq;
+  int tile = total - 1 - static_cast<int>(blockIdx.x), seq = -1, tok0 = 0, ntok = 0;
+  if (tile < 0) return;
   for (int s = 0; s < n_seqs; ++s) {
     const int c0 = cu_tokens[s], len = cu_tokens[s + 1] - c0, nt = (len + tq - 1) / tq;
     if (tile < nt) { seq = s; tok0 = c0 + tile * tq; ntok = min(tq, len - tile * tq); break; }
@@ -239,11 +243,12 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
   for (int i = tid; i < (kRows * QS + 2 * kKeys * QS + 2 * kKeys * VS) / 8; i += kThreads) reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   const int dch = a.dim / 8, vch = a.vdim / 8;     // 16-byte chunks per row
+  // the query rows travel with the first key tile's copy group (asynchronous: no thread waits for its own row here)
   for (int i = tid; i < kRows * dch; i += kThreads) {
     const int r = i / dch, c = i % dch, t = r / group, hr = r % group;
     if (t < ntok)
-      *reinterpret_cast<uint4*>(Qs + r * QS + c * 8) =
-          *reinterpret_cast<const uint4*>(qg + static_cast<int64_t>(tok0 + t) * a.ldq + static_cast<int64_t>(g * group + hr) * a.dim + c * 8);
+      cp_async_16(smem_u32(Qs + r * QS + c * 8),
+                  qg + static_cast<int64_t>(tok0 + t) * a.ldq + static_cast<int64_t>(g * group + hr) * a.dim + c * 8, 16);
   }
   // Cache slot of every key of a tile: looked up by 64 threads one tile ahead of the copy that needs it (the table read is a
   // dependent global load; in the copy loop it would serialise), kept in shared memory [2][64].

@@ -183,7 +183,7 @@ class Talapel : public ModelImpl {
     if (c["loop"].is_object()) {
       const int start = c["loop"]["start"].as_int(0), stop = c["loop"]["stop"].as_int(0), times = c["loop"]["times"].as_int(1);
       NVLLM_CHECK_ARG(0 <= start && start <= stop && stop <= n && times >= 0, NVLLM_ERR_ARG, "Talapel config: loop %d..%d x %d", start, stop, times);
-      has_loop_ = true;
+      has_loop_ = times > 0 && stop > start;   // only then does a pass begin somewhere and W_loop get used
       for (int i = 0; i < start; ++i) runs_.push_back({i, false});
       for (int t = 0; t < times; ++t)
         for (int i = start; i < stop; ++i) runs_.push_back({i, i == start});
@@ -403,6 +403,7 @@ class Talapel : public ModelImpl {
   int load_weight(const char* name_c, const void* src_v, int64_t rows, int64_t cols, cudaStream_t st) override {
     NVLLM_CHECK_ARG(name_c && src_v, NVLLM_ERR_ARG, "load_weight: NULL");
     const std::string name(name_c);
+    if (name == "loop.in" && !has_loop_) return 0;   // a checkpoint may carry it although no pass ever begins
     NVLLM_CHECK_ARG(needed_.count(name), NVLLM_ERR_ARG, "load_weight: tensor '%s' is not part of this model", name_c);
     const Target t = target_of(name);
     NVLLM_CHECK_ARG(t.kind >= 0, NVLLM_ERR_ARG, "load_weight: unknown tensor '%s'", name_c);
