@@ -734,7 +734,7 @@ TALAPEL_SIZES = {
 
 
 def talapel_config(z):
-    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "softcap": 30.0,
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "softcap": 50.0,
             "q_temp": {"coef": 0.1, "every": 256}}
     right = {"heads": z["s_heads"], "groups": z["s_groups"], "state": z["s_state"], "vdim": z["s_vdim"], "conv": z["taps"], "norm_groups": z["s_groups"]}
     par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0},
