@@ -195,8 +195,11 @@ __device__ __forceinline__ void attn_tile(float (&o)[VMAX / 8][4], float (&m)[2]
       s[nt][e] = p;
       l[e >> 1] += p;
     }
+  // once a row's running maximum has settled (soon, with capped scores) the factor is exactly 1: skip the rescaling then
+  if (!__all_sync(0xffffffffu, corr[0] == 1.0f && corr[1] == 1.0f)) {
 #pragma unroll
-  for (int i = 0; i < 2 * VP; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+    for (int i = 0; i < 2 * VP; ++i) { o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1]; }
+  }
 #pragma unroll
   for (int kc2 = 0; kc2 < NP; ++kc2) {
     uint32_t pf[4];
@@ -316,8 +319,11 @@ __global__ void __launch_bounds__(kThreads, 2) capped_attn_mma_kernel(const Attn
                                                     smem_u32(vb + kq * 16 * VS + vh * (VMAX / 2) + v_lane), key0, pos, qscale, capped, cap2,
                                                     key0 + 15 > min_pos, tq4);
     } else if (warp_has_rows) {
-      attn_tile<DMAX, VMAX, 4, VMAX / 16, QS, VS>(o, m, l, q_addr, smem_u32(kb + k_lane), smem_u32(vb + v_lane), kt * kKeys, pos, qscale, capped,
-                                                  cap2, kt * kKeys + kKeys - 1 > min_pos, tq4);
+      // two halves of 32 keys: half the score registers of a 64-key pass (no spills under the 128-register cap)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf)
+        attn_tile<DMAX, VMAX, 2, VMAX / 16, QS, VS>(o, m, l, q_addr, smem_u32(kb + hf * 32 * QS + k_lane), smem_u32(vb + hf * 32 * VS + v_lane),
+                                                    kt * kKeys + hf * 32, pos, qscale, capped, cap2, kt * kKeys + hf * 32 + 31 > min_pos, tq4);
     }
     if (tid < kKeys) slot_s[kt & 1][tid] = slot_ahead;   // tile kt's slots were consumed by load_tile(kt) an iteration ago
     __syncthreads();   // everyone is done with this buffer before the next load overwrites it

@@ -574,6 +574,27 @@ def test_greedy_generation_through_the_engine(cuda, tmp_path, dtype):
     assert st["decode_batches"] >= n_new - 1 and st["free_blocks"] == st["total_blocks"]
 
 
+def test_generation_survives_preemption(cuda, tmp_path):
+    """A cache pool too small for four growing sequences: the scheduler preempts (pages and state slot go back), later
+    admits the victim again and recomputes it from position 0 into whatever slot is free; the tokens stay the oracle's."""
+    from nano_vllm_rs_b200.engine import SamplingParams
+    rng = np.random.default_rng(16)
+    cfg = variant("all_kinds")
+    w = T.random_weights(cfg, rng)
+    prompts = [rng.integers(0, cfg["vocab"], 16).tolist() for _ in range(4)]
+    n_new = 40
+    eng, _ = make_engine(tmp_path, cfg, w, "float32", bs=16, blocks=11, max_seqs=4, eager=0)   # 4 x 56 tokens need 16 pages
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=n_new, ignore_eos=True))
+    st = eng.scheduler.get_stats()
+    assert st["preemptions"] > 0 and st["free_blocks"] == st["total_blocks"]
+    for p, o in zip(prompts, outs):
+        ref, margins = T.greedy(cfg, w, p, n_new)
+        for j in range(n_new):
+            if o[j] != ref[j]:
+                assert margins[j] < 1e-3, (j, margins[j])
+                break
+
+
 def test_trace_run_replays_a_schedule(cuda, tmp_path):
     rng = np.random.default_rng(14)
     cfg = variant("all_kinds")
