@@ -446,7 +446,7 @@ int nvllm_attn_bias_store(void* q, int64_t ldq, void* k_cache, void* v_cache, in
  *   s[t, h, j] = cap(scale * temp(p_t) * q[t, h] . k[j, h / (heads / kv_heads)]),  j <= p_t = positions[t] in sequence tok_seq[t]
  *   temp(p) = 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1),  cap(s) = softcap * tanh(s / softcap) (softcap <= 0: s)
  *   out[t, h, :] = sum_j softmax_j(s) v[j, ...] * sigmoid(gate[t, h, :])   (gate: f32, nullable)
- * Key size dim, value size vdim (<= 256).  block_tables: [sequences, table_cap].  cu_tokens (nullable): [n_seqs + 1] token
+ * Key size dim, value size vdim (<= 512).  block_tables: [sequences, table_cap].  cu_tokens (nullable): [n_seqs + 1] token
  * range of every sequence in the batch, tokens in order of position; with it, bf16 problems whose rows are 16-byte multiples
  * (dim, vdim <= 128) run on tensor cores, 64 (token, head) rows of one sequence and key / value head per CTA. */
 int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int64_t ldq, const float* gate, int64_t ldg,
@@ -462,7 +462,7 @@ int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int64_t ldq, c
  *
  * S_t = a_t S_(t-1) + b_t k_t v_t^T,  y_t = S_t^T q_t + skip_h v_t;  S: [dk, dv] per head; state: [slots, heads, dk, dv].
  * q, k: [n, groups * dk] (head h reads group h / (heads / groups)); v, y: [n, heads * dv]; decay / step: [n, heads] when
- * *_per_token, else [heads]; step nullable (1), skip nullable (0).  dk <= 256. */
+ * *_per_token, else [heads]; step nullable (1), skip nullable (0).  dk <= 512. */
 int nvllm_linear_recurrence(float* y, int64_t ldy, const float* q, int64_t ldq, const float* k, int64_t ldk, const float* v,
                             int64_t ldv, const float* decay, int32_t decay_per_token, const float* step,
                             int32_t step_per_token, const float* skip, float* state, const int32_t* seq_slot,

@@ -46,7 +46,7 @@ struct AttnArgs {
   float scale, softcap, temp_coef; int temp_every;
 };
 
-constexpr int kMaxVPerLane = 8;  // vdim <= 256
+constexpr int kMaxVPerLane = 16;  // vdim <= 512
 
 // One warp per (token, head): 32 keys per round, lane j scores key j (q broadcast from shared memory), the warp shares
 // the online-softmax statistics, then every lane accumulates its output dimensions over the 32 keys.
@@ -429,7 +429,7 @@ extern "C" int nvllm_capped_attention(void* out, int64_t ldo, const void* q, int
                                       const int32_t* cu_tokens, int32_t n_seqs, int32_t dtype, void* stream) {
   NVLLM_CHECK_ARG(n >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && dim > 0 && vdim > 0 && vdim <= 32 * kMaxVPerLane &&
                       dim <= 2048 && block_size > 0 && table_cap > 0 && temp_every > 0, NVLLM_ERR_ARG,
-                  "capped_attention: n=%d heads=%d/%d dim=%d vdim=%d (vdim <= 256)", n, heads, kv_heads, dim, vdim);
+                  "capped_attention: n=%d heads=%d/%d dim=%d vdim=%d (vdim <= 512)", n, heads, kv_heads, dim, vdim);
   NVLLM_CHECK_ARG(dtype == NVLLM_BF16 || dtype == NVLLM_F32, NVLLM_ERR_DTYPE, "capped_attention: dtype %d", dtype);
   if (n == 0) return 0;
   NVLLM_CHECK_ARG(out && q && k_cache && v_cache && tok_seq && positions && block_tables, NVLLM_ERR_ARG, "capped_attention: NULL");

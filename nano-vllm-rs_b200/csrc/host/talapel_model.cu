@@ -140,11 +140,11 @@ class Talapel : public ModelImpl {
         L.sH = s["heads"].need_int("right.heads"); L.sG = s["groups"].as_int(1);
         L.sN = s["state"].need_int("right.state"); L.sP = s["vdim"].need_int("right.vdim");
         L.taps = s["conv"].as_int(1); L.norm_groups = s["norm_groups"].as_int(1);
-        NVLLM_CHECK_ARG(L.H > 0 && L.G > 0 && L.H % L.G == 0 && L.D > 0 && L.V > 0 && L.V <= 256 && L.temp_every > 0, NVLLM_ERR_ARG,
-                        "Talapel config: layer %zu attention sizes (heads %d / %d, dim %d, vdim %d <= 256)", i, L.H, L.G, L.D, L.V);
-        NVLLM_CHECK_ARG(L.sH > 0 && L.sG > 0 && L.sH % L.sG == 0 && L.sN > 0 && L.sN <= 256 && L.sP > 0 && L.taps >= 1 && L.taps <= 16 &&
+        NVLLM_CHECK_ARG(L.H > 0 && L.G > 0 && L.H % L.G == 0 && L.D > 0 && L.V > 0 && L.V <= 512 && L.temp_every > 0, NVLLM_ERR_ARG,
+                        "Talapel config: layer %zu attention sizes (heads %d / %d, dim %d, vdim %d <= 512)", i, L.H, L.G, L.D, L.V);
+        NVLLM_CHECK_ARG(L.sH > 0 && L.sG > 0 && L.sH % L.sG == 0 && L.sN > 0 && L.sN <= 512 && L.sP > 0 && L.taps >= 1 && L.taps <= 16 &&
                             L.norm_groups > 0 && (L.sH * L.sP) % L.norm_groups == 0, NVLLM_ERR_ARG,
-                        "Talapel config: layer %zu state-space sizes (heads %d / %d, state %d <= 256, vdim %d, conv %d <= 16, norm_groups %d)",
+                        "Talapel config: layer %zu state-space sizes (heads %d / %d, state %d <= 512, vdim %d, conv %d <= 16, norm_groups %d)",
                         i, L.sH, L.sG, L.sN, L.sP, L.taps, L.norm_groups);
       } else if (type == "retention") {
         L.mix = kRetention;
@@ -152,9 +152,9 @@ class Talapel : public ModelImpl {
         L.rot_dims = m["rot"]["dims"].as_int(0);
         L.rot_base = m["rot"]["base"].as_double(10000.0);
         const json::Value& d = m["decay"];
-        NVLLM_CHECK_ARG(L.rH > 0 && L.rD > 0 && L.rD <= 256 && L.rV > 0 && L.rot_dims >= 0 && L.rot_dims % 2 == 0 && L.rot_dims <= L.rD &&
+        NVLLM_CHECK_ARG(L.rH > 0 && L.rD > 0 && L.rD <= 512 && L.rV > 0 && L.rot_dims >= 0 && L.rot_dims % 2 == 0 && L.rot_dims <= L.rD &&
                             L.rot_base > 0 && d.is_array() && static_cast<int>(d.size()) == L.rH, NVLLM_ERR_ARG,
-                        "Talapel config: layer %zu retention sizes (heads %d, dim %d <= 256, vdim %d, rot dims %d, one decay per head)", i,
+                        "Talapel config: layer %zu retention sizes (heads %d, dim %d <= 512, vdim %d, rot dims %d, one decay per head)", i,
                         L.rH, L.rD, L.rV, L.rot_dims);
         for (size_t k = 0; k < d.size(); ++k) L.decay_h.push_back(static_cast<float>(d[k].as_double(1.0)));
       } else {

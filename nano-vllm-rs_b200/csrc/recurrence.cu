@@ -383,8 +383,8 @@ extern "C" int nvllm_linear_recurrence(float* y, int64_t ldy, const float* q, in
                                        int32_t step_per_token, const float* skip, float* state, const int32_t* seq_slot,
                                        const int32_t* cu_tokens, const int64_t* positions, int32_t n_seqs, int32_t heads,
                                        int32_t groups, int32_t dk, int32_t dv, void* stream) {
-  NVLLM_CHECK_ARG(n_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dk <= 256 && dv > 0, NVLLM_ERR_ARG,
-                  "linear_recurrence: seqs=%d heads=%d groups=%d dk=%d (<= 256) dv=%d", n_seqs, heads, groups, dk, dv);
+  NVLLM_CHECK_ARG(n_seqs >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && dk > 0 && dk <= 512 && dv > 0, NVLLM_ERR_ARG,
+                  "linear_recurrence: seqs=%d heads=%d groups=%d dk=%d (<= 512) dv=%d", n_seqs, heads, groups, dk, dv);
   if (n_seqs == 0) return 0;
   NVLLM_CHECK_ARG(y && q && k && v && decay && state && seq_slot && cu_tokens && positions, NVLLM_ERR_ARG, "linear_recurrence: NULL");
   RecArgs a{y, ldy, q, k, v, ldq, ldk, ldv, heads / groups, decay, decay_per_token ? heads : 0, step, step_per_token ? heads : 0,
@@ -394,7 +394,8 @@ extern "C" int nvllm_linear_recurrence(float* y, int64_t ldy, const float* q, in
   if (dk <= 32) return launch_recurrence<32, 1, 2>(a, n_seqs, st);
   if (dk <= 64) return launch_recurrence<32, 2, 2>(a, n_seqs, st);
   if (dk <= 128) return launch_recurrence<32, 4, 2>(a, n_seqs, st);
-  return launch_recurrence<32, 8, 2>(a, n_seqs, st);
+  if (dk <= 256) return launch_recurrence<32, 8, 2>(a, n_seqs, st);
+  return launch_recurrence<32, 16, 2>(a, n_seqs, st);
 }
 
 extern "C" int nvllm_causal_conv(float* out, int64_t ldo, const float* in, int64_t ldi, const float* w, const float* bias, float* state,

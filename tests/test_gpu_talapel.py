@@ -124,7 +124,7 @@ def _attention_ref(q, keys, vals, m, pos):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,D,V", [(4, 2, 6, 10), (3, 3, 16, 16), (5, 1, 40, 33), (8, 2, 40, 88), (6, 2, 64, 32), (2, 1, 128, 128)])
+@pytest.mark.parametrize("H,G,D,V", [(4, 2, 6, 10), (3, 3, 16, 16), (5, 1, 40, 33), (8, 2, 40, 88), (6, 2, 64, 32), (2, 1, 128, 128), (1, 1, 12, 300)])
 def test_capped_attention_paged(cuda, dtype, H, G, D, V):
     """Prompt portions and single tokens of three sequences in one launch, pages in random order, query positions around the
     temperature steps and the page borders; biases, the gate and the cache store included.  bf16 with head sizes that are
@@ -237,7 +237,7 @@ def test_causal_conv_carries_its_last_inputs(cuda, taps):
         np.testing.assert_allclose(np.vstack(got[s]), ref[s], rtol=2e-5, atol=2e-5)
 
 
-@pytest.mark.parametrize("heads,groups,dk,dv", [(4, 2, 5, 4), (3, 3, 16, 7), (2, 1, 48, 40), (1, 1, 130, 33), (2, 2, 64, 64)])
+@pytest.mark.parametrize("heads,groups,dk,dv", [(4, 2, 5, 4), (3, 3, 16, 7), (2, 1, 48, 40), (1, 1, 130, 33), (2, 2, 64, 64), (1, 1, 300, 6)])
 def test_linear_recurrence_portions_and_slots(cuda, heads, groups, dk, dv):
     """S <- a S + b k v^T, y = S^T q + d v with per-token decay and step: three sequences in portions of changing size through
     reused slots against the token-by-token recurrence in float64."""
