@@ -64,7 +64,7 @@ struct Layer {
   float* norm1 = nullptr;
   void *a_in = nullptr, *a_o = nullptr, *s_in = nullptr, *s_o = nullptr, *r_in = nullptr, *r_o = nullptr;
   float *qb = nullptr, *kb = nullptr, *vb = nullptr, *ob = nullptr;
-  float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr, *s_norm = nullptr, *decay = nullptr;
+  float *conv_w = nullptr, *conv_b = nullptr, *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr, *s_norm = nullptr, *decay = nullptr, *kscale = nullptr;
   void *gu = nullptr, *down = nullptr, *eup = nullptr, *edown = nullptr;
   int32_t* table = nullptr;
   const float* rope = nullptr;
@@ -242,8 +242,10 @@ class Talapel : public ModelImpl {
         const std::string a = p + "mix.";
         RUN(oalloc(&L.r_in, static_cast<size_t>(pad8(L.r_cols())) * W, true)); RUN(oalloc(&L.r_o, W * L.rH * L.rV));
         for (const char* t : {"q", "k", "v", "g", "o"}) needed_.insert(a + t);
-        RUN(dalloc(&L.decay, L.rH));
+        RUN(dalloc(&L.decay, L.rH)); RUN(dalloc(&L.kscale, L.rH));
         NVLLM_CUDA(cudaMemcpy(L.decay, L.decay_h.data(), sizeof(float) * L.rH, cudaMemcpyHostToDevice));
+        const std::vector<float> ks(L.rH, 1.0f / sqrtf(static_cast<float>(L.rD)));   // k <- k dim^-1/2, applied as the recurrence's step
+        NVLLM_CUDA(cudaMemcpy(L.kscale, ks.data(), sizeof(float) * L.rH, cudaMemcpyHostToDevice));
         if (L.rot_dims > 0) {  // rotary table shared by the layers that agree on (base, dims)
           const auto key = std::make_pair(L.rot_base, L.rot_dims);
           auto it = rope_tables_.find(key);
@@ -542,13 +544,12 @@ class Talapel : public ModelImpl {
         pend.a[1] = right_out_; pend.s[1] = L.right_scale;
         pend.bias = L.ob; pend.sb = L.left_scale;
       } else {
-        // --- retention: [q | k | v | g] in one projection, rotary on q and k (k scaled), recurrence, per-head norm + gate, Wo
+        // --- retention: [q | k | v | g] in one projection, rotary on q and k, recurrence (k scaled), per-head norm + gate, Wo
         const int qn = L.rH * L.rD, vn = L.rH * L.rV, ldr = pad8(L.r_cols());
         RUN(lin(proj_, normed_, L.r_in, ldr, W, ldr, NVLLM_F32, "retention q k v g projection"));
-        RUN(nvllm_rotate_half(proj_, ldr, v.positions, L.rope, lim_.max_positions, N, L.rH, L.rD, L.rot_dims, 1.0f, st)); ++launches; mk("rotate_half (q)");
-        RUN(nvllm_rotate_half(proj_ + qn, ldr, v.positions, L.rope, lim_.max_positions, N, L.rH, L.rD, L.rot_dims,
-                              1.0f / sqrtf(static_cast<float>(L.rD)), st)); ++launches; mk("rotate_half (k)");
-        RUN(nvllm_linear_recurrence(y_, vn, proj_, ldr, proj_ + qn, ldr, proj_ + 2 * qn, ldr, L.decay, 0, nullptr, 0, nullptr, rs.ret, v.seq_slots,
+        // q and k heads lie side by side: one launch rotates both; the key scale dim^-1/2 rides in the recurrence as its step
+        RUN(nvllm_rotate_half(proj_, ldr, v.positions, L.rope, lim_.max_positions, N, 2 * L.rH, L.rD, L.rot_dims, 1.0f, st)); ++launches; mk("rotate_half (q, k)");
+        RUN(nvllm_linear_recurrence(y_, vn, proj_, ldr, proj_ + qn, ldr, proj_ + 2 * qn, ldr, L.decay, 0, L.kscale, 0, nullptr, rs.ret, v.seq_slots,
                                     v.cu_tokens, v.positions, S, L.rH, L.rH, L.rD, L.rV, st)); ++launches; mk("linear_recurrence (retention)");
         RUN(nvllm_gated_group_norm(mix_in_, vn, y_, vn, proj_ + 2 * qn + vn, ldr, nullptr, N, vn, L.rH, eps_, 0, dt_, st)); ++launches; mk("gated_group_norm");
         RUN(lin(left_out_, mix_in_, L.r_o, W, vn, W, NVLLM_F32, "retention output projection"));

@@ -348,6 +348,50 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(TO* __restrict__ 
   }
 }
 
+// The same with the part's values held in registers (one global pass): parts of up to 2048 values in 16-byte vectors.
+template <typename TO>
+__global__ void __launch_bounds__(128) gated_group_norm_vec_kernel(TO* __restrict__ out, int64_t ldo, const float* __restrict__ y, int64_t ldy,
+                                                                   const float* __restrict__ z, int64_t ldz, const float* __restrict__ w, int gs,
+                                                                   int parts, float eps, int gate_first) {
+  __shared__ float red[4];
+  const int64_t t = blockIdx.x / parts;
+  const int g = blockIdx.x % parts, nv = gs / 4;
+  const float4* yr = reinterpret_cast<const float4*>(y + t * ldy + static_cast<int64_t>(g) * gs);
+  const float4* zr = reinterpret_cast<const float4*>(z + t * ldz + static_cast<int64_t>(g) * gs);
+  float4 v[4], sg[4];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = threadIdx.x + 128 * k;
+    if (c < nv) {
+      v[k] = yr[c];
+      const float4 zz = zr[c];
+      sg[k] = make_float4(silu_f(zz.x), silu_f(zz.y), silu_f(zz.z), silu_f(zz.w));
+      if (gate_first) { v[k].x *= sg[k].x; v[k].y *= sg[k].y; v[k].z *= sg[k].z; v[k].w *= sg[k].w; }
+      sq += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  const float r = rsqrtf((red[0] + red[1] + red[2] + red[3]) / gs + eps);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int c = threadIdx.x + 128 * k;
+    if (c < nv) {
+      float4 o = make_float4(v[k].x * r, v[k].y * r, v[k].z * r, v[k].w * r);
+      if (!gate_first) { o.x *= sg[k].x; o.y *= sg[k].y; o.z *= sg[k].z; o.w *= sg[k].w; }
+      if (w) {
+        const float4 ww = reinterpret_cast<const float4*>(w + static_cast<int64_t>(g) * gs)[c];
+        o.x *= ww.x; o.y *= ww.y; o.z *= ww.z; o.w *= ww.w;
+      }
+      const int64_t at = t * ldo + static_cast<int64_t>(g) * gs + 4 * c;
+      if (sizeof(TO) == 2) *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + at) = make_uint2(pack_bf16x2(o.x, o.y), pack_bf16x2(o.z, o.w));
+      else *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at) = o;
+    }
+  }
+}
+
 inline unsigned grid_for(int64_t total) {
   int64_t b = (total + 255) / 256;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
@@ -457,6 +501,15 @@ extern "C" int nvllm_gated_group_norm(void* out, int64_t ldo, const float* y, in
   NVLLM_CHECK_ARG(out && y && gate, NVLLM_ERR_ARG, "gated_group_norm: NULL");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = static_cast<unsigned>(static_cast<int64_t>(n) * parts);
+  const int gs = cols / parts;
+  if (gs % 4 == 0 && gs <= 2048 && ldo % 4 == 0 && ldy % 4 == 0 && ldg % 4 == 0 && aligned16(out) && aligned16(y) && aligned16(gate) && aligned16(w)) {
+    if (out_dtype == NVLLM_BF16)
+      gated_group_norm_vec_kernel<bf16><<<grid, 128, 0, st>>>(static_cast<bf16*>(out), ldo, y, ldy, gate, ldg, w, gs, parts, eps, gate_first);
+    else
+      gated_group_norm_vec_kernel<float><<<grid, 128, 0, st>>>(static_cast<float*>(out), ldo, y, ldy, gate, ldg, w, gs, parts, eps, gate_first);
+    NVLLM_LAUNCH_CHECK("gated_group_norm_vec_kernel");
+    return 0;
+  }
   if (out_dtype == NVLLM_BF16)
     gated_group_norm_kernel<bf16><<<grid, 128, 0, st>>>(static_cast<bf16*>(out), ldo, y, ldy, gate, ldg, w, cols / parts, parts, eps, gate_first);
   else
