@@ -48,7 +48,7 @@ struct AttnArgs {
 
 constexpr int kMaxVPerLane = 16;  // vdim <= 512
 
-// One warp per (token, head): 32 keys per round, lane j scores key j (q broadcast from shared memory), the warp shares
+// One warp per (token, head): 32 keys per pass, lane j scores key j (q broadcast from shared memory), the warp shares
 // the online-softmax statistics, then every lane accumulates its output dimensions over the 32 keys.
 template <typename T>
 __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a) {
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
     const float mt = warp_max(s);
     const float mn = fmaxf(m, mt);
     if (mn == -INFINITY) continue;
-    const float corr = expf(m - mn);   // m = -inf on the first round: 0
+    const float corr = expf(m - mn);   // m = -inf on the first pass: 0
     const float p = s == -INFINITY ? 0.f : expf(s - mn);
     l = l * corr + warp_sum(p);
     m = mn;

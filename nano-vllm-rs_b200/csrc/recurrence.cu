@@ -33,7 +33,7 @@ struct RecArgs {
   int heads, dk, dv;
 };
 
-constexpr int kRecTile = 16;  // tokens staged per round
+constexpr int kRecTile = 16;  // tokens per stage
 
 __device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void* gptr) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr) : "memory");
@@ -41,8 +41,8 @@ __device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void* gptr)
 
 // CTA = (head, sequence, slice of dv).  Thread (pc, ns): PP neighbouring columns of the state, rows [ns * NPT, (ns + 1) * NPT) of
 // each in registers (every k / q value read from shared memory serves PP columns: the broadcast reads are what binds).
-// kRecTile tokens' k, q (rows of dk), v, a, b are staged in shared memory with cp.async, two rounds deep: the copies of the
-// next round fly while this round's tokens are stepped through, and the steps themselves need no synchronisation.  NSL row
+// kRecTile tokens' k, q (rows of dk), v, a, b are staged in shared memory with cp.async, two stages deep: the copies of the
+// next stage fly while the current stage's tokens are stepped through, and the steps themselves need no synchronisation.  NSL row
 // slices of one column sit in neighbouring lanes and are summed with shuffles.  vec: rows are 16-byte multiples.
 template <int NPT, int NSL, int PP>
 __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a, int pb, int vec) {
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(512) linear_recurrence_kernel(const RecArgs a,
         if (live[j] && ns == 0) a.y[(tb + tt) * a.ldy + static_cast<int64_t>(h) * a.dv + p + j * half] = fmaf(d, xv[j], acc[j]);
       }
     }
-    __syncthreads();   // the round after next overwrites this stage
+    __syncthreads();   // the copy issued in the next iteration overwrites this stage
   }
 #pragma unroll
   for (int j = 0; j < PP; ++j)
