@@ -596,6 +596,35 @@ def test_generation_survives_preemption(cuda, tmp_path):
                 break
 
 
+def test_command_line_generates_and_samples(cuda, tmp_path):
+    """`python -m nano_vllm_rs_b200 generate` on a Talapel checkpoint: greedy tokens are the oracle's; with a temperature the
+    device sampler draws from the same logits (tokens in range, two different prompts give different draws)."""
+    import sys
+    rng = np.random.default_rng(17)
+    cfg = variant("all_kinds")
+    w = T.random_weights(cfg, rng)
+    _, model_dir = make_engine(tmp_path, cfg, w, "float32")
+    prompt = rng.integers(0, cfg["vocab"], 9).tolist()
+    run = lambda *extra: subprocess.run([sys.executable, "-m", "nano_vllm_rs_b200", "generate", "--model", model_dir, "--dtype", "float32",
+                                         "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "12", "--block-size", "16", *extra],
+                                        cwd=ROOT, capture_output=True, text=True, timeout=600)
+    r = run()
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    ref, margins = T.greedy(cfg, w, prompt, 12)
+    assert out["prompt_ids"] == prompt and len(out["completion_ids"]) == 12
+    for j in range(12):
+        if out["completion_ids"][j] != ref[j]:
+            assert margins[j] < 1e-3
+            break
+    r = run("--temperature", "1.5", "--top-k", "20")
+    assert r.returncode == 0, r.stderr[-2000:]
+    sampled = json.loads(r.stdout.strip().splitlines()[-1])["completion_ids"]
+    assert len(sampled) == 12 and all(0 <= t < cfg["vocab"] for t in sampled) and sampled != ref
+    r = subprocess.run([sys.executable, "-m", "nano_vllm_rs_b200", "architectures"], cwd=ROOT, capture_output=True, text=True, timeout=120)
+    assert "Talapel" in r.stdout
+
+
 def test_trace_run_replays_a_schedule(cuda, tmp_path):
     rng = np.random.default_rng(14)
     cfg = variant("all_kinds")
