@@ -135,13 +135,10 @@ __global__ void __launch_bounds__(128) capped_attn_warp_kernel(const AttnArgs a)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kWarps = 8, kRows = 16 * kWarps, kKeys = 64, kThreads = 32 * kWarps;
 
-// One MUFU instruction, relative error 2^-11: an absolute error of |s| * 5e-4 on a capped score s, far inside what bf16 keys
-// and queries carry (4e-3 relative) -- used by the bf16 tensor-core kernel only.
-__device__ __forceinline__ float fast_tanh(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
+// tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1): two MUFU operations (ex2, rcp), absolute error ~1e-6; exact at both saturations
+// (2^inf -> 1, 2^-inf -> -1).  The one-instruction tanh.approx is 2^-11 relative: too coarse where two scores near the cap
+// compete (cap x 5e-4 apart in the exponent).
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, fast_exp2(x * (2.0f * kLog2e)) + 1.0f); }
 
 // One warp's share of a key tile: 16 rows x (16 NP) keys -> S on tensor cores, cap / mask / online softmax in f32, then
 // O[:, 0 .. 16 VP) += P . V.  k_addr / v_addr are the warp's ldmatrix lane addresses of its first key (and first value column).
