@@ -391,7 +391,7 @@ def variant(name):
     if name == "tensor_core":    # sizes the tensor-core GEMMs accept (bf16): width and inner sizes multiples of 64, experts of 64
         return T.make_config([("parallel", P(heads=2, kv_heads=1, dim=32, vdim=32, scale=0.2, softcap=10.0, coef=0.3, every=16, s_heads=4,
                                              groups=1, state=16, s_vdim=16, taps=4, norm_groups=2), T.expert_mlp(4, 2, 64)),
-                              ("retention", R(heads=2, dim=32, vdim=32, rot_dims=16, rot_base=1e4), T.dense_mlp(64))],
+                              ("retention", R(heads=2, dim=32, vdim=32, rot_dims=16, rot_base=1e4), T.dense_mlp(128))],   # 128: SiLU gate in the GEMM epilogue
                              width=64, vocab=96, loop=(0, 2, 3))
     raise KeyError(name)
 
