@@ -1,5 +1,5 @@
 // capped_attn.cu — grouped-query softmax attention over a paged key / value cache with
-//   * no rotary: position enters through a per-position query temperature  1 + coef * ln(floor((p + 1) / every) + 1),
+//   * no rotary: the only positional signal is a query temperature  1 + coef * ln(floor((p + 1) / every) + 1),
 //   * a soft cap on the scores:  s <- cap * tanh(s / cap)   (cap <= 0: none),
 //   * an optional output gate:   out *= sigmoid(gate)       (gate: f32 pre-activations, same layout as the output),
 //   * key and value sizes that may differ (dim, vdim).

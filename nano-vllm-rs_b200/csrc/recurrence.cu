@@ -7,8 +7,8 @@
 //   nvllm_linear_recurrence   S_t = a_t S_(t-1) + b_t k_t v_t^T,   y_t = S_t^T q_t + d v_t        (S: [dk, dv] per head)
 //       covers state-space duality (k = B, q = C, v = x, a = exp(-exp(A_log) dt), b = dt, d = D; B and C shared by the heads
 //       of a group) and retention (a = a constant per head, b = 1, d = 0)
-//   nvllm_causal_conv         per-channel convolution over the last `taps` tokens (+ bias, SiLU); the raw inputs of the last
-//       taps - 1 tokens are part of the state
+//   nvllm_causal_conv         per-channel convolution over the last `taps` tokens (+ bias, SiLU); the slot keeps the window's
+//       history, i.e. the raw inputs of the preceding taps - 1 tokens
 //   nvllm_ssd_prepare         dt = softplus(raw + bias), a = exp(-exp(A_log) dt)
 //   nvllm_rotate_half         rotary positions, dimension i paired with i + dims/2, on the first `dims` values of every head
 //   nvllm_gated_group_norm    RMS norm over equal parts of a row with a SiLU gate before or after it
